@@ -57,11 +57,13 @@ class RunSpec:
 
     `cache_of is None` means the run owns a cache (and writes it).  Otherwise it
     is the index, in the schedule, of an earlier run whose cache this run reads
-    without writing.
+    without writing.  `add_embedding`: the embedding's output (the residual stream as it was
+    before the first run) is added to the stream once more right in front of this run.
     """
 
     layer: int
     cache_of: int | None = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -87,6 +89,8 @@ class ModelSpec:
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"schedule[{i}] names layer {run.layer}, "
                                  f"but there are {len(self.layers)} layers")
+            if run.add_embedding and i == 0:
+                raise ValueError("schedule[0] cannot add the embedding's output again")
             if run.cache_of is not None:
                 if not 0 <= run.cache_of < i:
                     raise ValueError(f"schedule[{i}].cache_of={run.cache_of} must "

@@ -1,7 +1,14 @@
-// Mixture of experts whose routing is a table: token id -> `top` experts.
+// Mixture of experts.  Which experts a token uses is a table row of `top` expert numbers: the row of
+// its token id in a table of the model (ids given), or its own row of a table that a router filled
+// for this step (ids null).
 //
-//   route:    for every (token, k) pair ("entry" t * top + k) the expert table[id[t], k]; entries are
+//   router:   softmax over the router's logits, a correction added for the choice only, the best
+//             `keep` of `count` groups of neighbouring experts by their best member, the `top` best
+//             members of those; the weights are the softmax values of the chosen.
+//   route:    for every (token, k) pair ("entry" t * top + k) the expert table[row, k]; entries are
 //             grouped by expert (a counting sort in one CTA) and the groups are cut into row tiles.
+//             Experts numbered E and above have no matrices ("identity experts": their output is
+//             their input); their entries are placed behind the others and get no tile.
 //   grouped product: one CTA per (row tile of an expert's entries, tile of output columns),
 //             C = A W_e^T with float32 FMAs, every output summed over K in ascending order, so an
 //             entry's result does not depend on the tile it fell into or on the rest of the step.
@@ -11,7 +18,8 @@
 //             own expert (bfloat16, 16-byte loads, two rows a warp), with the same two epilogues.
 //   gather / activation: what stands around the library's grouped product in prompt-sized
 //             bfloat16 steps: the rows in the grouped order, and the experts' gated activation.
-//   combine:  out[t] = weight * sum_k y[row of entry t * top + k] (+ the shared expert's rows), float32.
+//   combine:  out[t] = weight * sum_k y[row of entry t * top + k] (+ the shared expert's rows), float32;
+//             or with a weight per entry, an identity expert's entry adding weight * x[t].
 //
 // A product over all rows with one weight matrix (a shared expert) is the same kernel with one
 // group.  Everything is decided on the device: the launches depend on the step's layout only.
@@ -29,43 +37,43 @@ constexpr int kMoeThreads = 256;
 // ids grouped by expert; tile_expert / tile_row0: int32 [max_tiles], n_tiles: int32 [1];
 // place: int32 [n_entries] the sorted position of every entry (the inverse of `sorted`).
 __global__ void moe_route_kernel(const int* __restrict__ ids, const int* __restrict__ table, int T,
-                                 int top, int E, int* __restrict__ offsets, int* __restrict__ sorted,
+                                 int top, int E, int E_all, int* __restrict__ offsets, int* __restrict__ sorted,
                                  int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                                  int* __restrict__ n_tiles, int max_tiles, int* __restrict__ place) {
-    extern __shared__ int sm[];          // counts [E], cursor [E]
+    extern __shared__ int sm[];          // counts [E_all], cursor [E_all]
     int* counts = sm;
-    int* cursor = sm + E;
+    int* cursor = sm + E_all;
     pdl_launch_dependents();
     pdl_wait();
     const int n = T * top;
-    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    for (int e = threadIdx.x; e < E_all; e += blockDim.x) counts[e] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const int e = table[static_cast<size_t>(ids[i / top]) * top + i % top];
-        if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+        const int e = table[static_cast<size_t>(ids != nullptr ? ids[i / top] : i / top) * top + i % top];
+        if (e >= 0 && e < E_all) atomicAdd(&counts[e], 1);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0, tiles = 0;
-        for (int e = 0; e < E; ++e) {
-            offsets[e] = at;
+        for (int e = 0; e < E_all; ++e) {
+            if (e <= E) offsets[e] = at;
             cursor[e] = at;
-            for (int r = 0; r < counts[e] && tiles < max_tiles; r += kMoeBM) {
+            for (int r = 0; e < E && r < counts[e] && tiles < max_tiles; r += kMoeBM) {
                 tile_expert[tiles] = e;
                 tile_row0[tiles] = at + r;
                 ++tiles;
             }
             at += counts[e];
         }
-        offsets[E] = at;
+        if (E_all == E) offsets[E] = at;
         *n_tiles = tiles;
     }
     __syncthreads();
     // one atomic per entry places it in its expert's group; the order inside a group changes no
     // result (each entry's row is computed by itself)
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const int e = table[static_cast<size_t>(ids[i / top]) * top + i % top];
-        if (e >= 0 && e < E) {
+        const int e = table[static_cast<size_t>(ids != nullptr ? ids[i / top] : i / top) * top + i % top];
+        if (e >= 0 && e < E_all) {
             const int pos = atomicAdd(&cursor[e], 1);
             sorted[pos] = i;
             place[i] = pos;
@@ -92,10 +100,11 @@ __global__ void moe_gather_rows_kernel(const T* __restrict__ a, long long a_stri
 }
 
 // The experts' activation over a product whose columns alternate gate_j, up_j:
-// out[r, j] = g * sigmoid(alpha * g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit).
+// out[r, j] = g * sigmoid(alpha * g) * (u + shift), g = min(gate, limit), u = clamp(up, -limit, limit)
+// (limit = infinity, alpha = 1, shift = 0: silu(gate) * up).
 template <typename T>
 __global__ void clamped_gate_up_kernel(const T* __restrict__ gu, T* __restrict__ out, int ff,
-                                       long long n, float limit, float alpha) {
+                                       long long n, float limit, float alpha, float shift) {
     pdl_launch_dependents();
     pdl_wait();
     if (sizeof(T) == 2 && (n & 3) == 0 && ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
@@ -111,7 +120,7 @@ __global__ void clamped_gate_up_kernel(const T* __restrict__ gu, T* __restrict__
             for (int e = 0; e < 4; ++e) {
                 const float g = fminf(__low2float(h[e]), limit);
                 const float u = fminf(fmaxf(__high2float(h[e]), -limit), limit);
-                y[e] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+                y[e] = g / (1.0f + expf(-alpha * g)) * (u + shift);
             }
             const __nv_bfloat162 y01 = __floats2bfloat162_rn(y[0], y[1]), y23 = __floats2bfloat162_rn(y[2], y[3]);
             uint2 packed;
@@ -125,7 +134,7 @@ __global__ void clamped_gate_up_kernel(const T* __restrict__ gu, T* __restrict__
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const float g = fminf(to_float(gu[2 * i]), limit);
         const float u = fminf(fmaxf(to_float(gu[2 * i + 1]), -limit), limit);
-        out[i] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+        out[i] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + shift));
     }
 }
 
@@ -141,12 +150,12 @@ __global__ void __launch_bounds__(kGemvWarps * 32)
 moe_gemv_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, int a_div,
                 const __nv_bfloat16* __restrict__ W, const int* __restrict__ ids,
                 const int* __restrict__ table, int top, int E, void* __restrict__ out, int N, int K,
-                float limit, float alpha) {
+                float limit, float alpha, float shift) {
     extern __shared__ float xs[];                          // [K]
     pdl_launch_dependents();
     pdl_wait();
     const int entry = blockIdx.y;
-    const int expert = table[static_cast<size_t>(ids[entry / top]) * top + entry % top];
+    const int expert = table[static_cast<size_t>(ids != nullptr ? ids[entry / top] : entry / top) * top + entry % top];
     if (expert < 0 || expert >= E) return;
     const __nv_bfloat16* x = A + static_cast<size_t>(entry / a_div) * a_stride;
     for (int i = threadIdx.x; i < K; i += blockDim.x) xs[i] = __bfloat162float(x[i]);
@@ -181,7 +190,7 @@ moe_gemv_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, int a_d
                 const float g = fminf(a0, limit);
                 const float u = fminf(fmaxf(a1, -limit), limit);
                 static_cast<__nv_bfloat16*>(out)[static_cast<size_t>(entry) * (N / 2) + row / 2] =
-                    __float2bfloat16_rn(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+                    __float2bfloat16_rn(g / (1.0f + expf(-alpha * g)) * (u + shift));
             } else {
                 float* o = static_cast<float*>(out) + static_cast<size_t>(entry) * N;
                 o[row] = a0;
@@ -193,7 +202,7 @@ moe_gemv_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, int a_d
 
 // MODE 0: out (TO) rows at `scatter` positions (or the sorted position itself), N columns.
 // MODE 1: W's rows alternate gate_j, up_j; g = min(gate, limit), u = clamp(up, -limit, limit);
-//         out[pos, j] = g * sigmoid(alpha * g) * (u + 1), N / 2 columns.
+//         out[pos, j] = g * sigmoid(alpha * g) * (u + shift), N / 2 columns.
 template <typename T, typename TO, int MODE>
 __global__ void __launch_bounds__(kMoeThreads)
 grouped_gemm_kernel(const T* __restrict__ A, long long a_stride, const int* __restrict__ gather,
@@ -201,7 +210,7 @@ grouped_gemm_kernel(const T* __restrict__ A, long long a_stride, const int* __re
                     const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                     const int* __restrict__ n_tiles, int n_rows_single, TO* __restrict__ out,
                     long long out_stride, const int* __restrict__ scatter, int N, int K, float limit,
-                    float alpha) {
+                    float alpha, float shift) {
     __shared__ float As[kMoeBK][kMoeBM + 1];
     __shared__ float Ws[kMoeBK][kMoeBN + 1];
     __shared__ int rows_s[kMoeBM];
@@ -281,7 +290,7 @@ grouped_gemm_kernel(const T* __restrict__ A, long long a_stride, const int* __re
                 if (c + 1 < N) {
                     const float g = fminf(acc[i][j], limit);
                     const float u = fminf(fmaxf(acc[i][j + 1], -limit), limit);
-                    const float y = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+                    const float y = g / (1.0f + expf(-alpha * g)) * (u + shift);
                     out[static_cast<size_t>(pos) * out_stride + c / 2] = from_float<TO>(y);
                 }
             }
@@ -336,6 +345,121 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
     }
 }
 
+
+// ------------------------------------------------------------------- router
+// One warp per token.  s = softmax(logits[t, 0..n)) (float32); choice = s + correction (null: s);
+// the n outputs form `count` equal groups of neighbours, a group's score is its largest choice, and
+// only members of the `keep` best groups can be chosen (count <= 1: all can); the `top` largest
+// choices among those are written to chosen[t, 0..top) in falling order, their s to weight[t, ..].
+// Equal values go to the lower index.
+__global__ void moe_router_select_kernel(const float* __restrict__ logits, long long l_stride,
+                                         const float* __restrict__ correction, int n, int count,
+                                         int keep, int top, int* __restrict__ chosen,
+                                         float* __restrict__ weight, int T) {
+    extern __shared__ float rs[];            // per warp: s [n], choice [n], group score [count]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    const int groups = count > 1 ? count : 1;
+    float* sv = rs + static_cast<size_t>(warp) * (2 * n + groups);
+    float* cv = sv + n;
+    float* gv = cv + n;
+    const float* z = logits + static_cast<size_t>(t) * l_stride;
+    float m = -INFINITY;
+    for (int i = lane; i < n; i += 32) m = fmaxf(m, z[i]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int i = lane; i < n; i += 32) {
+        const float e = expf(z[i] - m);
+        sv[i] = e;
+        sum += e;
+    }
+    sum = warp_sum(sum);
+    for (int i = lane; i < n; i += 32) {
+        const float p = sv[i] / sum;
+        sv[i] = p;
+        cv[i] = correction != nullptr ? p + correction[i] : p;
+    }
+    __syncwarp();
+    if (count > 1 && keep < count) {
+        const int size = n / count;
+        for (int g = lane; g < count; g += 32) {
+            float best = -INFINITY;
+            for (int i = 0; i < size; ++i) best = fmaxf(best, cv[g * size + i]);
+            gv[g] = best;
+        }
+        __syncwarp();
+        // the (count - keep) worst groups leave: the best `keep` stay, marked by +infinity
+        for (int round = 0; round < keep; ++round) {
+            float best = -INFINITY;
+            int arg = 0x7fffffff;
+            for (int g = lane; g < count; g += 32) {
+                const float v = gv[g];
+                if (v != INFINITY && (v > best || (v == best && g < arg))) { best = v; arg = g; }
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+            }
+            if (lane == 0 && arg != 0x7fffffff) gv[arg] = INFINITY;
+            __syncwarp();
+        }
+        for (int i = lane; i < n; i += 32)
+            if (gv[i / size] != INFINITY) cv[i] = -INFINITY;
+        __syncwarp();
+    }
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int i = lane; i < n; i += 32) {
+            const float v = cv[i];
+            if (!isnan(v) && (v > best || (v == best && i < arg))) { best = v; arg = i; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg == 0x7fffffff) arg = 0;
+        if (lane == 0) {
+            chosen[static_cast<size_t>(t) * top + k] = arg;
+            weight[static_cast<size_t>(t) * top + k] = sv[arg];
+            cv[arg] = NAN;                    // taken: not chosen again
+        }
+        __syncwarp();
+    }
+}
+
+// out[t, c] = sum_k weight[t, k] * (table[t, k] < E ? y[row(t * top + k), c] : x[t, c]); float32.
+// row(e) = place[e] where the rows of y are in the grouped order, else e.  The sum runs over k in
+// ascending order.
+template <typename TY, typename TX>
+__global__ void moe_combine_weighted_kernel(const TY* __restrict__ y, const int* __restrict__ place,
+                                            const int* __restrict__ table,
+                                            const float* __restrict__ weight, const TX* __restrict__ x,
+                                            int E, int top, int H, long long n, float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long t = i / H;
+        const int c = static_cast<int>(i - t * H);
+        float s = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const long long e = t * top + k;
+            const int expert = table[e];
+            const float v = (expert >= 0 && expert < E)
+                                ? to_float(y[(place != nullptr ? place[e] : e) * H + c])
+                                : to_float(x[i]);
+            s = fmaf(weight[e], v, s);
+        }
+        out[i] = s;
+    }
+}
+
 }  // namespace somi
 
 using namespace somi;
@@ -344,18 +468,19 @@ SOMI_API int somi_moe_row_tile() { return kMoeBM; }
 
 // work: int32 [(E + 1) + n_entries + 2 * max_tiles + 1 + n_entries]: offsets, sorted, tile_expert,
 // tile_row0, n_tiles, place
-SOMI_API int somi_moe_route(const int* ids, const int* table, int T, int top, int E, int* work,
-                            int max_tiles, cudaStream_t stream) {
+// Table entries in [E, E_all) are experts without matrices: placed behind the others, no tiles.
+SOMI_API int somi_moe_route(const int* ids, const int* table, int T, int top, int E, int E_all,
+                            int* work, int max_tiles, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (top <= 0 || E <= 0 || E > 4096) return SOMI_ERR_UNSUPPORTED;
+    if (top <= 0 || E <= 0 || E_all < E || E_all > 4096) return SOMI_ERR_UNSUPPORTED;
     int* offsets = work;
     int* sorted = offsets + E + 1;
     int* tile_expert = sorted + static_cast<size_t>(T) * top;
     int* tile_row0 = tile_expert + max_tiles;
     int* n_tiles = tile_row0 + max_tiles;
     int* place = n_tiles + 1;
-    launch_pdl(moe_route_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * E, stream, ids, table, T, top,
-               E, offsets, sorted, tile_expert, tile_row0, n_tiles, max_tiles, place);
+    launch_pdl(moe_route_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * E_all, stream, ids, table, T,
+               top, E, E_all, offsets, sorted, tile_expert, tile_row0, n_tiles, max_tiles, place);
     return launch_status();
 }
 
@@ -375,17 +500,17 @@ SOMI_API int somi_moe_gather_rows(const void* a, int dtype, long long a_stride, 
 }
 
 SOMI_API int somi_clamped_gate_up(const void* gu, void* out, int dtype, long long rows, int ff,
-                                  float limit, float alpha, cudaStream_t stream) {
+                                  float limit, float alpha, float shift, cudaStream_t stream) {
     const long long n = rows * ff;
     if (n <= 0) return 0;
     const int blocks = static_cast<int>(((n + 255) / 256) < 148LL * 16 ? ((n + 255) / 256) : 148LL * 16);
     if (dtype == SOMI_F32)
         launch_pdl(clamped_gate_up_kernel<float>, dim3(blocks), dim3(256), 0, stream,
-                   static_cast<const float*>(gu), static_cast<float*>(out), ff, n, limit, alpha);
+                   static_cast<const float*>(gu), static_cast<float*>(out), ff, n, limit, alpha, shift);
     else
         launch_pdl(clamped_gate_up_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
                    static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), ff, n,
-                   limit, alpha);
+                   limit, alpha, shift);
     return launch_status();
 }
 
@@ -393,7 +518,7 @@ SOMI_API int somi_clamped_gate_up(const void* gu, void* out, int dtype, long lon
 // float32 rows [entries, N].  Row e of A is a[e / a_div].
 SOMI_API int somi_moe_gemv(const void* A, long long a_stride, int a_div, const void* W, const int* ids,
                            const int* table, int top, int E, int n_entries, void* out, int N, int K,
-                           int mode, float limit, float alpha, cudaStream_t stream) {
+                           int mode, float limit, float alpha, float shift, cudaStream_t stream) {
     if (n_entries <= 0) return 0;
     if (K <= 0 || (K & 7) || N <= 0 || (mode == 1 && (N & 1)) || K > 40 * 1024 ||
         (reinterpret_cast<uintptr_t>(W) & 15))
@@ -405,13 +530,13 @@ SOMI_API int somi_moe_gemv(const void* A, long long a_stride, int a_div, const v
             cudaFuncSetAttribute(moe_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         launch_pdl(moe_gemv_kernel<1>, grid, dim3(kGemvWarps * 32), smem, stream,
                    static_cast<const __nv_bfloat16*>(A), a_stride, a_div,
-                   static_cast<const __nv_bfloat16*>(W), ids, table, top, E, out, N, K, limit, alpha);
+                   static_cast<const __nv_bfloat16*>(W), ids, table, top, E, out, N, K, limit, alpha, shift);
     } else {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(moe_gemv_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         launch_pdl(moe_gemv_kernel<0>, grid, dim3(kGemvWarps * 32), smem, stream,
                    static_cast<const __nv_bfloat16*>(A), a_stride, a_div,
-                   static_cast<const __nv_bfloat16*>(W), ids, table, top, E, out, N, K, limit, alpha);
+                   static_cast<const __nv_bfloat16*>(W), ids, table, top, E, out, N, K, limit, alpha, shift);
     }
     return launch_status();
 }
@@ -423,7 +548,7 @@ SOMI_API int somi_grouped_gemm(const void* A, int dtype, long long a_stride, int
                                int use_gather, const void* W, const int* work, int E, int n_entries,
                                int max_tiles, int n_rows, void* out, int out_f32,
                                long long out_stride, int use_scatter, int N, int K, int mode,
-                               float limit, float alpha, cudaStream_t stream) {
+                               float limit, float alpha, float shift, cudaStream_t stream) {
     if (N <= 0 || K <= 0) return SOMI_ERR_UNSUPPORTED;
     const int* offsets = nullptr; const int* sorted = nullptr; const int* tile_expert = nullptr;
     const int* tile_row0 = nullptr; const int* n_tiles = nullptr;
@@ -447,7 +572,7 @@ SOMI_API int somi_grouped_gemm(const void* A, int dtype, long long a_stride, int
     launch_pdl(grouped_gemm_kernel<TT, TO, MODE>, grid, dim3(kMoeThreads), 0, stream,            \
                static_cast<const TT*>(A), a_stride, gather, gather_div, static_cast<const TT*>(W), \
                offsets, tile_expert, tile_row0, n_tiles, n_rows, static_cast<TO*>(out), out_stride, \
-               scatter, N, K, limit, alpha)
+               scatter, N, K, limit, alpha, shift)
     if (dtype == SOMI_F32) {
         if (mode == 1) SOMI_LAUNCH_GG(float, float, 1);
         else SOMI_LAUNCH_GG(float, float, 0);
@@ -471,5 +596,39 @@ SOMI_API int somi_moe_combine(const void* y, int y_dtype, const int* place, cons
     else
         launch_pdl(moe_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
                    static_cast<const __nv_bfloat16*>(y), place, extra, weight, top, H, n, out);
+    return launch_status();
+}
+
+// logits: float32 [T, l_stride] (n columns read); chosen int32 [T, top], weight float32 [T, top].
+SOMI_API int somi_moe_router_select(const float* logits, long long l_stride, const float* correction,
+                                    int T, int n, int count, int keep, int top, int* chosen,
+                                    float* weight, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (n <= 0 || n > 4096 || top <= 0 || top > n || (count > 1 && (n % count || keep <= 0 || keep > count)))
+        return SOMI_ERR_UNSUPPORTED;
+    if (count > 1 && keep < count && top > keep * (n / count)) return SOMI_ERR_UNSUPPORTED;
+    const int warps = 4;
+    const size_t smem = sizeof(float) * warps * (2 * n + (count > 1 ? count : 1));
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(moe_router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(moe_router_select_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), smem, stream,
+               logits, l_stride, correction, n, count, keep, top, chosen, weight, T);
+    return launch_status();
+}
+
+SOMI_API int somi_moe_combine_weighted(const void* y, int y_dtype, const int* place, const int* table,
+                                       const float* weight, const void* x, int x_dtype, int E, int top,
+                                       int T, int H, float* out, cudaStream_t stream) {
+    const long long n = static_cast<long long>(T) * H;
+    if (n <= 0) return 0;
+    const int blocks = static_cast<int>(((n + 255) / 256) < 148LL * 16 ? ((n + 255) / 256) : 148LL * 16);
+#define SOMI_LAUNCH_CW(TY, TX)                                                                    \
+    launch_pdl(moe_combine_weighted_kernel<TY, TX>, dim3(blocks), dim3(256), 0, stream,           \
+               static_cast<const TY*>(y), place, table, weight, static_cast<const TX*>(x), E, top, H, n, out)
+    if (y_dtype == SOMI_F32 && x_dtype == SOMI_F32) SOMI_LAUNCH_CW(float, float);
+    else if (y_dtype == SOMI_F32) SOMI_LAUNCH_CW(float, __nv_bfloat16);
+    else if (x_dtype == SOMI_F32) SOMI_LAUNCH_CW(__nv_bfloat16, float);
+    else SOMI_LAUNCH_CW(__nv_bfloat16, __nv_bfloat16);
+#undef SOMI_LAUNCH_CW
     return launch_status();
 }

@@ -1,0 +1,573 @@
+// Kernels of layers whose branches run side by side and of mixers that carry a matrix state:
+//   * residual += mult * (scale_a * a + scale_b * b), then one or two RMS norms of the same row
+//     (a layer whose mixer and feed-forward both read the stream they both add to)
+//   * RMS norm of every query and key head with a weight, rotation of the halves of a head's
+//     first `rot` entries, cache write (keys and values of different widths)
+//   * the recurrence of a matrix state per head, S <- decay * S + k u^T, o = S^T q, with
+//     u = v (a decayed sum of outer products) or u = beta (v - S^T k) (the gated delta rule),
+//     the decay a constant per head or a number per key channel and token
+//   * RMS norm in equal parts of a row, times a weight, times the sigmoid of a gate
+//   * half the sum of two rows, each RMS-normed with a weight of its own
+//   * the square of relu
+// Norms, angles, gates, decays, step sizes and the state are float32; inputs and outputs are float32
+// or bfloat16.
+#include "common.cuh"
+#include "vec4.cuh"
+
+namespace somi {
+
+__device__ __forceinline__ float sigmoid32(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus32(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float silu32(float z) { return z / (1.0f + expf(-z)); }
+
+// ------------------------------------- scaled sum of two branches + one or two RMS norms
+// d_a = sum_s a[s][row] (partial sums `a_stride` apart, added in order), d_b likewise;
+// r = residual[row] + mult * (scale_a .* d_a + scale_b .* d_b) + extra[row]   (an absent branch
+// or absent extra rows add nothing);
+// if write_back: residual[row] = r;  out1[i] = r / sqrt(mean(r^2) + eps) * w1, out2 likewise with
+// w2 (either may be absent); row = rows ? rows[i] : i.  The row lives in shared memory.
+__global__ void add_scaled_rmsnorm_kernel(float* __restrict__ residual, const void* __restrict__ a,
+                                          int a_dtype, int a_splits, long long a_stride,
+                                          const void* __restrict__ scale_a, const void* __restrict__ b,
+                                          int b_dtype, int b_splits, long long b_stride,
+                                          const void* __restrict__ scale_b, int scale_dtype, float mult,
+                                          const float* __restrict__ extra,
+                                          const void* __restrict__ w1, const void* __restrict__ w2,
+                                          int w_dtype, float eps, void* __restrict__ out1,
+                                          void* __restrict__ out2, int out_dtype,
+                                          const int* __restrict__ rows, int H, int write_back, int vec4) {
+    extern __shared__ __align__(16) float row_buf[];
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i_out = blockIdx.x;
+    const int row = rows ? rows[i_out] : i_out;
+    float* res = residual + static_cast<size_t>(row) * H;
+    const size_t base = static_cast<size_t>(row) * H;
+    float ss = 0.f;
+    if (vec4) {
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            F4 r = load4(res + i);
+            F4 t = F4{{0.f, 0.f, 0.f, 0.f}};
+            if (a != nullptr) {
+                F4 d = load4_any(a, a_dtype, base + i);
+                for (int s = 1; s < a_splits; ++s) {
+                    const F4 e = load4_any(a, a_dtype, static_cast<size_t>(s) * a_stride + base + i);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) d.v[c] += e.v[c];
+                }
+                if (scale_a != nullptr) {
+                    const F4 sc = load4_any(scale_a, scale_dtype, i);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) d.v[c] *= sc.v[c];
+                }
+                t = d;
+            }
+            if (b != nullptr) {
+                F4 d = load4_any(b, b_dtype, base + i);
+                for (int s = 1; s < b_splits; ++s) {
+                    const F4 e = load4_any(b, b_dtype, static_cast<size_t>(s) * b_stride + base + i);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) d.v[c] += e.v[c];
+                }
+                if (scale_b != nullptr) {
+                    const F4 sc = load4_any(scale_b, scale_dtype, i);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) d.v[c] *= sc.v[c];
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) t.v[c] += d.v[c];
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) r.v[c] = fmaf(mult, t.v[c], r.v[c]);
+            if (extra != nullptr) {
+                const F4 x = load4(extra + base + i);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) r.v[c] += x.v[c];
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) ss = fmaf(r.v[c], r.v[c], ss);
+            store4(row_buf + i, r);
+            if (write_back && (a != nullptr || b != nullptr || extra != nullptr)) store4(res + i, r);
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float t = 0.f;
+            if (a != nullptr) {
+                float d = load_as_float(a, a_dtype, base + i);
+                for (int s = 1; s < a_splits; ++s)
+                    d += load_as_float(a, a_dtype, static_cast<size_t>(s) * a_stride + base + i);
+                if (scale_a != nullptr) d *= load_as_float(scale_a, scale_dtype, i);
+                t = d;
+            }
+            if (b != nullptr) {
+                float d = load_as_float(b, b_dtype, base + i);
+                for (int s = 1; s < b_splits; ++s)
+                    d += load_as_float(b, b_dtype, static_cast<size_t>(s) * b_stride + base + i);
+                if (scale_b != nullptr) d *= load_as_float(scale_b, scale_dtype, i);
+                t += d;
+            }
+            float r = fmaf(mult, t, res[i]);
+            if (extra != nullptr) r += extra[base + i];
+            row_buf[i] = r;
+            if (write_back && (a != nullptr || b != nullptr || extra != nullptr)) res[i] = r;
+            ss = fmaf(r, r, ss);
+        }
+    }
+    if (out1 == nullptr && out2 == nullptr) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / static_cast<float>(H) + eps);
+    const size_t obase = static_cast<size_t>(i_out) * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = row_buf[i] * inv;
+        if (out1 != nullptr) {
+            const float y = v * load_as_float(w1, w_dtype, i);
+            if (out_dtype == SOMI_F32) static_cast<float*>(out1)[obase + i] = y;
+            else static_cast<__nv_bfloat16*>(out1)[obase + i] = __float2bfloat16_rn(y);
+        }
+        if (out2 != nullptr) {
+            const float y = v * load_as_float(w2, w_dtype, i);
+            if (out_dtype == SOMI_F32) static_cast<float*>(out2)[obase + i] = y;
+            else static_cast<__nv_bfloat16*>(out2)[obase + i] = __float2bfloat16_rn(y);
+        }
+    }
+}
+
+// --------------------------- per-head RMS norm + rotation of halves + cache write
+// A row of `qkv` holds nq query heads and nkv key heads of `hd` elements and nkv value heads of
+// `vd` elements.  Every query and key head is divided by its root mean square over hd (eps inside
+// the root) and multiplied by `q_w` / `k_w` (hd elements, shared by the heads; null: no norm);
+// then entry i < rot/2 and entry i + rot/2 of the token at position p turn by p * inv_freq[i]
+// (the angle is formed and reduced in float64, its sine and cosine are float32); entries from
+// `rot` on pass.  Queries are written back in place; keys and values go to their cache slots.
+// One warp per head; the normed head passes through shared memory so that a lane finds its partner.
+template <typename T>
+__global__ void headnorm_rotary_store_kernel(T* __restrict__ qkv, long long stride,
+                                             const int* __restrict__ positions,
+                                             const double* __restrict__ inv_freq, int nq, int nkv,
+                                             int hd, int vd, int rot, const void* __restrict__ q_w,
+                                             const void* __restrict__ k_w, int w_dtype, float eps,
+                                             const int* __restrict__ slot_map, T* __restrict__ kcache,
+                                             T* __restrict__ vcache, int page_size) {
+    extern __shared__ float heads_s[];                 // [warps][hd]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    T* row = qkv + static_cast<size_t>(t) * stride;
+    const double pos = static_cast<double>(positions[t]);
+    const int slot = slot_map != nullptr ? slot_map[t] : -1;
+    const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+    float* mine = heads_s + warp * hd;
+    const int half = rot >> 1;
+    for (int head = blockIdx.y * nwarps + warp; head < nq + nkv; head += nwarps * gridDim.y) {
+        T* x = row + static_cast<size_t>(head) * hd;
+        const void* w = head < nq ? q_w : k_w;
+        float ss = 0.f;
+        for (int e = lane; e < hd; e += 32) {
+            const float v = to_float(x[e]);
+            mine[e] = v;
+            ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        if (w != nullptr) {
+            const float r = 1.0f / sqrtf(ss / static_cast<float>(hd) + eps);
+            for (int e = lane; e < hd; e += 32) mine[e] = mine[e] * r * load_as_float(w, w_dtype, e);
+        }
+        __syncwarp();
+        T* dst = nullptr;
+        if (head < nq) dst = x;
+        else if (slot >= 0) dst = kcache + ((page * nkv + (head - nq)) * page_size + off) * hd;
+        if (dst != nullptr) {
+            for (int e = lane; e < hd; e += 32) {
+                float v = mine[e];
+                if (e < rot) {
+                    const int i = e < half ? e : e - half;
+                    double angle = pos * inv_freq[i];
+                    angle -= 6.283185307179586476925286766559 * rint(angle * 0.15915494309189533576888376337251);
+                    float sn, cs;
+                    sincosf(static_cast<float>(angle), &sn, &cs);
+                    v = e < half ? fmaf(v, cs, -(mine[e + half] * sn)) : fmaf(v, cs, mine[e - half] * sn);
+                }
+                dst[e] = from_float<T>(v);
+            }
+        }
+        __syncwarp();
+    }
+    if (slot >= 0 && blockIdx.y == 0) {
+        const T* vrow = row + static_cast<size_t>(nq + nkv) * hd;
+        for (int g = 0; g < nkv; ++g) {
+            T* dst = vcache + ((page * nkv + g) * page_size + off) * vd;
+            for (int e = threadIdx.x; e < vd; e += blockDim.x) dst[e] = vrow[static_cast<size_t>(g) * vd + e];
+        }
+    }
+}
+
+// ------------------------------------------------------- matrix-state recurrence
+// Per request r and head h a state S [dk, dv] float32 in the request's slot; per token, in order:
+//     S <- g .* S         g: decay[h] (a constant), or per key channel i
+//                         g_i = exp(-exp(a_log[h]) * softplus(a[t, h dk + i] + dt_bias[h dk + i]))
+//     u = v                                   (DELTA false)
+//     u = sigmoid(b[t, h]) * (v - S^T k)      (DELTA true)
+//     S <- S + k u^T;   y[t, h, :] = S^T q.
+// q and k of head h are head h / (heads / qk_heads) of their tensors.  With `act_silu` q, k and v
+// pass SiLU as they are read; with `unit` q and k are divided by sqrt(sum of squares + unit_eps)
+// and q is multiplied by q_scale.
+// A CTA owns kRecCols columns of S for one (request, head) and walks through the request's rows
+// of this step, kRecBlock rows staged in shared memory at a time.  A column is held by 8 lanes,
+// lane l the rows l + 8 i; the sums over rows are taken in a fixed order (i ascending in a lane,
+// then a butterfly over the 8 lanes), so y does not depend on how the rows were cut into steps.
+constexpr int kRecLanes = 8;
+constexpr int kRecWarps = 4;
+constexpr int kRecColsPerWarp = 32 / kRecLanes;
+constexpr int kRecCols = kRecWarps * kRecColsPerWarp;
+constexpr int kRecBlock = 8;
+constexpr int kRecThreads = kRecWarps * 32;
+
+template <typename T, int R, bool DELTA>
+__global__ void __launch_bounds__(kRecThreads)
+matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                         long long q_stride, long long k_stride, long long v_stride, int act_silu,
+                         int unit, float unit_eps, float q_scale, const T* __restrict__ beta,
+                         long long beta_stride, const float* __restrict__ a, long long a_stride,
+                         const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                         const float* __restrict__ decay, float* __restrict__ state,
+                         const int* __restrict__ cu_q, const int* __restrict__ state_slot,
+                         float* __restrict__ y, int heads, int qk_heads, int dk, int dv) {
+    constexpr int DP = R * kRecLanes;                    // padded key width
+    __shared__ float q_s[kRecBlock][DP];
+    __shared__ float k_s[kRecBlock][DP];
+    __shared__ float g_s[kRecBlock][DP];
+    __shared__ float v_s[kRecBlock][kRecCols];
+    __shared__ float b_s[kRecBlock];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x, h = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sub = lane % kRecLanes;
+    const int col = blockIdx.z * kRecCols + warp * kRecColsPerWarp + lane / kRecLanes;
+    const int col_local = warp * kRecColsPerWarp + lane / kRecLanes;
+    const int qkh = h / (heads / qk_heads);
+    const bool channel_decay = a != nullptr;
+    const float rate = channel_decay ? expf(a_log[h]) : 0.f;
+    const float head_decay = channel_decay ? 1.f : decay[h];
+    float* st = state + (static_cast<size_t>(state_slot[r]) * heads + h) * dk * dv;
+    float s[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int row = sub + kRecLanes * i;
+        s[i] = (row < dk && col < dv) ? st[static_cast<size_t>(row) * dv + col] : 0.f;
+    }
+    const int first = cu_q[r], last = cu_q[r + 1];
+    for (int t0 = first; t0 < last; t0 += kRecBlock) {
+        const int n_tok = min(kRecBlock, last - t0);
+        __syncthreads();                                   // the block before has been read
+        for (int idx = tid; idx < n_tok * DP; idx += kRecThreads) {
+            const int tok = idx / DP, i = idx - tok * DP;
+            float qv = 0.f, kv = 0.f, gv = 1.f;
+            if (i < dk) {
+                const size_t t = static_cast<size_t>(t0 + tok);
+                qv = to_float(q[t * q_stride + static_cast<size_t>(qkh) * dk + i]);
+                kv = to_float(k[t * k_stride + static_cast<size_t>(qkh) * dk + i]);
+                if (act_silu) { qv = silu32(qv); kv = silu32(kv); }
+                if (channel_decay) {
+                    const size_t c = static_cast<size_t>(h) * dk + i;
+                    gv = expf(-rate * softplus32(a[t * a_stride + c] + dt_bias[c]));
+                } else {
+                    gv = head_decay;
+                }
+            }
+            q_s[tok][i] = qv;
+            k_s[tok][i] = kv;
+            g_s[tok][i] = gv;
+        }
+        for (int idx = tid; idx < n_tok * kRecCols; idx += kRecThreads) {
+            const int tok = idx / kRecCols, c = idx - tok * kRecCols;
+            const int cc = blockIdx.z * kRecCols + c;
+            float vv = 0.f;
+            if (cc < dv) {
+                vv = to_float(v[static_cast<size_t>(t0 + tok) * v_stride + static_cast<size_t>(h) * dv + cc]);
+                if (act_silu) vv = silu32(vv);
+            }
+            v_s[tok][c] = vv;
+        }
+        if (DELTA && tid < n_tok) b_s[tid] = sigmoid32(to_float(beta[static_cast<size_t>(t0 + tid) * beta_stride + h]));
+        __syncthreads();
+        if (unit) {
+            // a warp per row: q and k become unit vectors; the sum over the head in lane order
+            for (int tok = warp; tok < n_tok; tok += kRecWarps) {
+                float sq = 0.f, sk = 0.f;
+                for (int i = lane; i < dk; i += 32) {
+                    sq = fmaf(q_s[tok][i], q_s[tok][i], sq);
+                    sk = fmaf(k_s[tok][i], k_s[tok][i], sk);
+                }
+                sq = warp_sum(sq);
+                sk = warp_sum(sk);
+                const float rq = q_scale / sqrtf(sq + unit_eps), rk = 1.0f / sqrtf(sk + unit_eps);
+                for (int i = lane; i < dk; i += 32) {
+                    q_s[tok][i] *= rq;
+                    k_s[tok][i] *= rk;
+                }
+            }
+            __syncthreads();
+        }
+        for (int tok = 0; tok < n_tok; ++tok) {
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                const int row = sub + kRecLanes * i;
+                s[i] *= g_s[tok][row];
+                if (DELTA) dot = fmaf(s[i], k_s[tok][row], dot);
+            }
+            float u = v_s[tok][col_local];
+            if (DELTA) {
+#pragma unroll
+                for (int o = kRecLanes / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                u = b_s[tok] * (u - dot);
+            }
+            float out = 0.f;
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                const int row = sub + kRecLanes * i;
+                s[i] = fmaf(k_s[tok][row], u, s[i]);
+                out = fmaf(s[i], q_s[tok][row], out);
+            }
+#pragma unroll
+            for (int o = kRecLanes / 2; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+            if (sub == 0 && col < dv)
+                y[static_cast<size_t>(t0 + tok) * heads * dv + static_cast<size_t>(h) * dv + col] = out;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int row = sub + kRecLanes * i;
+        if (row < dk && col < dv) st[static_cast<size_t>(row) * dv + col] = s[i];
+    }
+}
+
+// ------------------------------------------- RMS norm in parts, weight, sigmoid gate
+// The C columns of y[t] in `groups` equal parts of n = C / groups, each divided by its own root
+// mean square; out = that * weight[c % w_len] * sigmoid(gate[t, c]) (gate null: no gate; its rows
+// lie `g_stride` elements apart).  One CTA per (token, part).
+template <typename TO>
+__global__ void group_rmsnorm_gate_kernel(const float* __restrict__ y, const void* __restrict__ gate,
+                                          int g_dtype, long long g_stride,
+                                          const void* __restrict__ weight, int w_dtype, int w_len,
+                                          float eps, TO* __restrict__ out, int C, int groups) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, part = blockIdx.y;
+    const int n = C / groups, c0 = part * n;
+    const float* yr = y + static_cast<size_t>(t) * C + c0;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(yr[i], yr[i], ss);
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / static_cast<float>(n) + eps);
+    TO* o = out + static_cast<size_t>(t) * C + c0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = yr[i] * r * load_as_float(weight, w_dtype, (c0 + i) % w_len);
+        if (gate != nullptr) v *= sigmoid32(load_as_float(gate, g_dtype, static_cast<size_t>(t) * g_stride + c0 + i));
+        o[i] = from_float<TO>(v);
+    }
+}
+
+// ------------------------------------------- half the sum of two normed rows
+// out[t] = 0.5 * (a[t] / rms(a[t]) * wa + b[t] / rms(b[t]) * wb), float32.  `a` and `b` may be
+// float32 partial sums (`*_splits` slices `*_stride` apart, added in order).  One CTA per token;
+// the two rows live in shared memory.
+__global__ void rmsnorm_pair_mean_kernel(const void* __restrict__ a, int a_dtype, int a_splits,
+                                         long long a_stride, const void* __restrict__ b, int b_dtype,
+                                         int b_splits, long long b_stride,
+                                         const void* __restrict__ wa, const void* __restrict__ wb,
+                                         int w_dtype, float eps, float* __restrict__ out, int H) {
+    extern __shared__ float pair_rows[];                  // a [H], b [H]
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t base = static_cast<size_t>(blockIdx.x) * H;
+    float* ra_s = pair_rows;
+    float* rb_s = pair_rows + H;
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float x = load_as_float(a, a_dtype, base + i);
+        for (int s = 1; s < a_splits; ++s) x += load_as_float(a, a_dtype, static_cast<size_t>(s) * a_stride + base + i);
+        float z = load_as_float(b, b_dtype, base + i);
+        for (int s = 1; s < b_splits; ++s) z += load_as_float(b, b_dtype, static_cast<size_t>(s) * b_stride + base + i);
+        ra_s[i] = x;
+        rb_s[i] = z;
+        sa = fmaf(x, x, sa);
+        sb = fmaf(z, z, sb);
+    }
+    sa = block_sum(sa, scratch);
+    sb = block_sum(sb, scratch);
+    const float ra = 1.0f / sqrtf(sa / static_cast<float>(H) + eps);
+    const float rb = 1.0f / sqrtf(sb / static_cast<float>(H) + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float x = ra_s[i] * ra * load_as_float(wa, w_dtype, i);
+        const float z = rb_s[i] * rb * load_as_float(wb, w_dtype, i);
+        out[base + i] = 0.5f * (x + z);
+    }
+}
+
+// ---------------------------------------------------------------- relu squared
+template <typename T>
+__global__ void relu2_kernel(const T* __restrict__ x, T* __restrict__ out, long long n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const float z = fmaxf(to_float(x[i]), 0.f);
+        out[i] = from_float<T>(z * z);
+    }
+}
+
+}  // namespace somi
+
+using namespace somi;
+
+static inline int threads_for(int n) { return min(256, max(32, ((n + 31) / 32) * 32)); }
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+SOMI_API int somi_add_scaled_rmsnorm(float* residual, const void* a, int a_dtype, int a_splits,
+                                     long long a_stride, const void* scale_a, const void* b,
+                                     int b_dtype, int b_splits, long long b_stride,
+                                     const void* scale_b, int scale_dtype, float mult,
+                                     const float* extra, const void* w1, const void* w2, int w_dtype, float eps, void* out1, void* out2,
+                                     int out_dtype, const int* rows, int n_out, int H, int write_back,
+                                     cudaStream_t stream) {
+    if (n_out <= 0) return 0;
+    if ((a_splits > 1 && a_dtype != SOMI_F32) || (b_splits > 1 && b_dtype != SOMI_F32))
+        return SOMI_ERR_UNSUPPORTED;
+    const size_t smem = sizeof(float) * H;
+    if (smem > 200 * 1024) return SOMI_ERR_UNSUPPORTED;
+    const int vec4 = (H & 3) == 0 && aligned16(residual) && aligned16(a) && aligned16(b) &&
+                     aligned16(scale_a) && aligned16(scale_b) && aligned16(extra) && (a_stride & 3) == 0 &&
+                     (b_stride & 3) == 0;
+    const int threads = vec4 ? min(1024, max(32, (((n_out <= 512 ? H / 4 : H / 16) + 31) / 32) * 32))
+                             : threads_for(H / 2);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(add_scaled_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem);
+    launch_pdl(add_scaled_rmsnorm_kernel, dim3(n_out), dim3(threads), smem, stream, residual, a,
+               a_dtype, a_splits, a_stride, scale_a, b, b_dtype, b_splits, b_stride, scale_b,
+               scale_dtype, mult, extra, w1, w2, w_dtype, eps, out1, out2, out_dtype, rows, H,
+               write_back, vec4);
+    return launch_status();
+}
+
+SOMI_API int somi_headnorm_rotary_store(void* qkv, int dtype, long long stride, const int* positions,
+                                        const double* inv_freq, int T, int nq, int nkv, int hd, int vd,
+                                        int rot, const void* q_w, const void* k_w, int w_dtype,
+                                        float eps, const int* slot_map, void* kcache, void* vcache,
+                                        int page_size, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (hd <= 0 || hd > 1024 || vd <= 0 || rot < 0 || rot > hd || (rot & 1) || nq <= 0 || nkv <= 0)
+        return SOMI_ERR_UNSUPPORTED;
+    const int warps = min(8, nq + nkv);
+    const dim3 grid(T, T <= 256 ? (nq + nkv + 7) / 8 : 1);
+    const size_t smem = sizeof(float) * warps * hd;
+    if (dtype == SOMI_F32)
+        launch_pdl(headnorm_rotary_store_kernel<float>, grid, dim3(32 * warps), smem, stream,
+                   static_cast<float*>(qkv), stride, positions, inv_freq, nq, nkv, hd, vd, rot, q_w,
+                   k_w, w_dtype, eps, slot_map, static_cast<float*>(kcache),
+                   static_cast<float*>(vcache), page_size);
+    else
+        launch_pdl(headnorm_rotary_store_kernel<__nv_bfloat16>, grid, dim3(32 * warps), smem, stream,
+                   static_cast<__nv_bfloat16*>(qkv), stride, positions, inv_freq, nq, nkv, hd, vd,
+                   rot, q_w, k_w, w_dtype, eps, slot_map, static_cast<__nv_bfloat16*>(kcache),
+                   static_cast<__nv_bfloat16*>(vcache), page_size);
+    return launch_status();
+}
+
+SOMI_API int somi_matrix_state_scan_max_key() { return 32 * kRecLanes; }
+
+// q, k: [T, *_stride] with qk_heads heads of dk elements from the pointer on; v: heads heads of dv.
+// delta != 0: beta [T, beta_stride] logits per head, of q's dtype.  a != null: float32 [T, a_stride]
+// decay logits per head and key channel with dt_bias [heads * dk] and a_log [heads]; else
+// decay [heads].  state: float32 [slots, heads, dk, dv]; y: float32 [T, heads * dv].
+SOMI_API int somi_matrix_state_scan(const void* q, const void* k, const void* v, int dtype,
+                                    long long q_stride, long long k_stride, long long v_stride,
+                                    int act_silu, int unit, float unit_eps, float q_scale, int delta,
+                                    const void* beta, long long beta_stride, const float* a,
+                                    long long a_stride, const float* dt_bias, const float* a_log,
+                                    const float* decay, float* state, const int* cu_q,
+                                    const int* state_slot, float* y, int R, int heads, int qk_heads,
+                                    int dk, int dv, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (dk <= 0 || dk > 32 * kRecLanes || dv <= 0 || heads <= 0 || qk_heads <= 0 || heads % qk_heads ||
+        (delta && beta == nullptr) || (a == nullptr && decay == nullptr) ||
+        (a != nullptr && (dt_bias == nullptr || a_log == nullptr)))
+        return SOMI_ERR_UNSUPPORTED;
+    dim3 grid(R, heads, (dv + kRecCols - 1) / kRecCols);
+    const int rows = (dk + kRecLanes - 1) / kRecLanes;
+#define SOMI_LAUNCH_REC(TT, RR, DD)                                                               \
+    launch_pdl(matrix_state_scan_kernel<TT, RR, DD>, grid, dim3(kRecThreads), 0, stream,          \
+               static_cast<const TT*>(q), static_cast<const TT*>(k), static_cast<const TT*>(v),   \
+               q_stride, k_stride, v_stride, act_silu, unit, unit_eps, q_scale,                 \
+               static_cast<const TT*>(beta), beta_stride,                                         \
+               a, a_stride, dt_bias, a_log, decay, state, cu_q, state_slot, y, heads, qk_heads, dk, dv)
+#define SOMI_REC_BY_ROWS(TT, DD)                                                                  \
+    do {                                                                                          \
+        if (rows <= 2) SOMI_LAUNCH_REC(TT, 2, DD);                                                \
+        else if (rows <= 4) SOMI_LAUNCH_REC(TT, 4, DD);                                           \
+        else if (rows <= 8) SOMI_LAUNCH_REC(TT, 8, DD);                                           \
+        else if (rows <= 16) SOMI_LAUNCH_REC(TT, 16, DD);                                         \
+        else SOMI_LAUNCH_REC(TT, 32, DD);                                                         \
+    } while (0)
+    if (dtype == SOMI_F32) {
+        if (delta) SOMI_REC_BY_ROWS(float, true);
+        else SOMI_REC_BY_ROWS(float, false);
+    } else {
+        if (delta) SOMI_REC_BY_ROWS(__nv_bfloat16, true);
+        else SOMI_REC_BY_ROWS(__nv_bfloat16, false);
+    }
+#undef SOMI_REC_BY_ROWS
+#undef SOMI_LAUNCH_REC
+    return launch_status();
+}
+
+SOMI_API int somi_group_rmsnorm_gate(const float* y, const void* gate, int g_dtype, long long g_stride,
+                                     const void* weight, int w_dtype, int w_len, float eps, void* out,
+                                     int out_dtype, int T, int C, int groups, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (groups <= 0 || C % groups || w_len <= 0) return SOMI_ERR_UNSUPPORTED;
+    const int threads = threads_for(C / groups);
+    if (out_dtype == SOMI_F32)
+        launch_pdl(group_rmsnorm_gate_kernel<float>, dim3(T, groups), dim3(threads), 0, stream, y, gate,
+                   g_dtype, g_stride, weight, w_dtype, w_len, eps, static_cast<float*>(out), C, groups);
+    else
+        launch_pdl(group_rmsnorm_gate_kernel<__nv_bfloat16>, dim3(T, groups), dim3(threads), 0, stream,
+                   y, gate, g_dtype, g_stride, weight, w_dtype, w_len, eps,
+                   static_cast<__nv_bfloat16*>(out), C, groups);
+    return launch_status();
+}
+
+SOMI_API int somi_rmsnorm_pair_mean(const void* a, int a_dtype, int a_splits, long long a_stride,
+                                    const void* b, int b_dtype, int b_splits, long long b_stride,
+                                    const void* wa, const void* wb, int w_dtype, float eps,
+                                    float* out, int T, int H, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if ((a_splits > 1 && a_dtype != SOMI_F32) || (b_splits > 1 && b_dtype != SOMI_F32))
+        return SOMI_ERR_UNSUPPORTED;
+    const size_t smem = sizeof(float) * 2 * H;
+    if (smem > 200 * 1024) return SOMI_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(rmsnorm_pair_mean_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem);
+    launch_pdl(rmsnorm_pair_mean_kernel, dim3(T), dim3(threads_for(H)), smem, stream, a, a_dtype,
+               a_splits, a_stride, b, b_dtype, b_splits, b_stride, wa, wb, w_dtype, eps, out, H);
+    return launch_status();
+}
+
+SOMI_API int somi_relu2(const void* x, void* out, int dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int blocks = static_cast<int>(((n + 255) / 256) < 148LL * 16 ? ((n + 255) / 256) : 148LL * 16);
+    if (dtype == SOMI_F32)
+        launch_pdl(relu2_kernel<float>, dim3(blocks), dim3(256), 0, stream,
+                   static_cast<const float*>(x), static_cast<float*>(out), n);
+    else
+        launch_pdl(relu2_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                   static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), n);
+    return launch_status();
+}

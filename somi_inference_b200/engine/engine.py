@@ -17,7 +17,7 @@ import torch
 from ..cache import CacheManager, OutOfPages
 from ..config import load_config
 from ..parts import BuildContext, Decoder, declared_tensors
-from ..weights import load_tensors
+from ..weights import load_tensors, tensor_shapes
 from .batch import BatchBuilder, StepBatch, StepEntry
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
@@ -92,6 +92,9 @@ class Engine:
         `max_tokens` tokens (rounded up to whole pages) when that is given.
         """
         config = load_config(model_dir)
+        if hasattr(config, "with_shapes"):
+            # sizes that config.json leaves to the tensors' shapes
+            config = config.with_shapes(tensor_shapes(model_dir))
         spec = config.to_model_spec()
         tensors = load_tensors(model_dir, declared_tensors(spec))
         self._setup(config, tensors, dtype=dtype, page_size=page_size, num_pages=num_pages,
@@ -116,6 +119,8 @@ class Engine:
             from ..ops import cuda_ops
             ops = cuda_ops()
         self.ops = ops
+        if hasattr(config, "with_shapes"):
+            config = config.with_shapes({name: tuple(t.shape) for name, t in tensors.items()})
         self.config = config
         self.spec = config.to_model_spec()
         ctx = BuildContext(dtype=self.dtype, device=self.device, ops=ops)

@@ -841,19 +841,25 @@ class CudaOps:
             trace.note("gated_group_rmsnorm", y.numel() * (4 + 2 * out.element_size()))
 
     # ------------------------------------------------------------ mixture of experts
-    def moe_route(self, token_ids, table, num_experts: int) -> tuple[torch.Tensor, int]:
+    def moe_route(self, token_ids, table, num_experts: int, all_experts: int | None = None
+                  ) -> tuple[torch.Tensor, int]:
         """Group the step's (token, k) entries by the expert that `table` [vocab, top] gives each
-        token id.  Returns the device work area that `grouped_product` reads and its tile bound."""
+        token id (`token_ids` None: `table` [T, top] holds the step's own rows, as a router wrote
+        them).  Experts numbered `num_experts` up to `all_experts` have no matrices: their entries
+        are placed behind the others and get no tile.  Returns the device work area that
+        `grouped_product` reads and its tile bound."""
         _check(token_ids, table)
-        assert token_ids.dtype == torch.int32 and table.dtype == torch.int32
-        T, top = token_ids.shape[0], table.shape[1]
+        assert (token_ids is None or token_ids.dtype == torch.int32) and table.dtype == torch.int32
+        T = table.shape[0] if token_ids is None else token_ids.shape[0]
+        top = table.shape[1]
         bm = int(self.lib.somi_moe_row_tile())
         max_tiles = -(-T * top // bm) + num_experts
         work = torch.empty(num_experts + 1 + 2 * T * top + 2 * max_tiles + 1, dtype=torch.int32,
-                           device=token_ids.device)
+                           device=table.device)
         rc = self.lib.somi_moe_route(_ptr(token_ids), _ptr(table), ctypes.c_int(T), ctypes.c_int(top),
-                                     ctypes.c_int(num_experts), _ptr(work), ctypes.c_int(max_tiles),
-                                     self._stream())
+                                     ctypes.c_int(num_experts),
+                                     ctypes.c_int(all_experts if all_experts else num_experts),
+                                     _ptr(work), ctypes.c_int(max_tiles), self._stream())
         self._done(rc, "moe_route")
         if trace.active():
             trace.note("moe_route", 12 * T * top)
@@ -865,9 +871,10 @@ class CudaOps:
 
         `route` = (work, max_tiles) from `moe_route` (None: one group, w [1, N, K], all rows).
         `gather`: row p of the grouped order reads a[entry(p) // top] (else a[p]); `scatter`: it
-        writes out[entry(p)] (else out[p]).  `gated` = (limit, alpha): w's rows alternate gate,
-        up and the result is g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit),
-        u = clamp(up, -limit, limit), N / 2 columns wide.  Products are float32 FMAs summed over K
+        writes out[entry(p)] (else out[p]).  `gated` = (limit, alpha[, shift = 1]): w's rows
+        alternate gate, up and the result is g * sigmoid(alpha * g) * (u + shift) with
+        g = min(gate, limit), u = clamp(up, -limit, limit), N / 2 columns wide (limit infinite,
+        alpha 1, shift 0: silu(gate) * up).  Products are float32 FMAs summed over K
         in ascending order."""
         _check(a, w)
         E, N, K = w.shape
@@ -882,7 +889,7 @@ class CudaOps:
         cols = N // 2 if gated is not None else N
         out_dtype = torch.float32 if (out_float32 and gated is None) else a.dtype
         out = torch.empty((n_rows, cols), dtype=out_dtype, device=a.device)
-        limit, alpha = gated if gated is not None else (0.0, 0.0)
+        limit, alpha, shift = self._gated(gated)
         rc = self.lib.somi_grouped_gemm(
             _ptr(a), _code(a), ctypes.c_longlong(a.stride(0)), ctypes.c_int(top),
             ctypes.c_int(1 if gather else 0), _ptr(w), _ptr(work), ctypes.c_int(E),
@@ -890,13 +897,20 @@ class CudaOps:
             ctypes.c_int(1 if out_dtype == torch.float32 else 0), ctypes.c_longlong(cols),
             ctypes.c_int(1 if scatter else 0), ctypes.c_int(N), ctypes.c_int(K),
             ctypes.c_int(1 if gated is not None else 0), ctypes.c_float(limit), ctypes.c_float(alpha),
-            self._stream())
+            ctypes.c_float(shift), self._stream())
         self._done(rc, "grouped_product")
         if trace.active():
             trace.note("grouped_product", (min(E, n_rows) * N * K + n_rows * K) * a.element_size()
                        + out.numel() * out.element_size(), 2.0 * n_rows * N * K,
                        detail=f"E={E} rows={n_rows} N={N} K={K}")
         return out
+
+    @staticmethod
+    def _gated(gated) -> tuple[float, float, float]:
+        """(limit, alpha, shift) of a gated activation; the shift is 1 where it is not given."""
+        if gated is None:
+            return 0.0, 0.0, 0.0
+        return float(gated[0]), float(gated[1]), float(gated[2]) if len(gated) > 2 else 1.0
 
     @staticmethod
     def _route_parts(route, E: int):
@@ -919,15 +933,15 @@ class CudaOps:
             trace.note("moe_gather_rows", 2 * out.numel() * out.element_size())
         return out
 
-    def clamped_gate_up(self, gu, limit: float, alpha: float) -> torch.Tensor:
-        """Columns of `gu` alternate gate, up: g * sigmoid(alpha * g) * (u + 1) with
+    def clamped_gate_up(self, gu, limit: float, alpha: float, shift: float = 1.0) -> torch.Tensor:
+        """Columns of `gu` alternate gate, up: g * sigmoid(alpha * g) * (u + shift) with
         g = min(gate, limit), u = clamp(up, -limit, limit); float32 arithmetic."""
         _check(gu)
         ff = gu.shape[1] // 2
         out = torch.empty((gu.shape[0], ff), dtype=gu.dtype, device=gu.device)
         rc = self.lib.somi_clamped_gate_up(_ptr(gu), _ptr(out), _code(gu), ctypes.c_longlong(gu.shape[0]),
                                            ctypes.c_int(ff), ctypes.c_float(limit), ctypes.c_float(alpha),
-                                           self._stream())
+                                           ctypes.c_float(shift), self._stream())
         self._done(rc, "clamped_gate_up")
         if trace.active():
             trace.note("clamped_gate_up", 3 * out.numel() * out.element_size())
@@ -946,19 +960,20 @@ class CudaOps:
         _check(a, w, token_ids, table)
         E, N, K = w.shape
         top = table.shape[1]
-        n = token_ids.shape[0] * top
+        n_tokens = table.shape[0] if token_ids is None else token_ids.shape[0]
+        n = n_tokens * top
         assert a.dtype == w.dtype == torch.bfloat16 and a.shape[1] == K
-        assert a.shape[0] == (token_ids.shape[0] if per_token else n)
+        assert a.shape[0] == (n_tokens if per_token else n)
         if gated is not None:
             out = torch.empty((n, N // 2), dtype=torch.bfloat16, device=a.device)
         else:
             out = torch.empty((n, N), dtype=torch.float32, device=a.device)
-        limit, alpha = gated if gated is not None else (0.0, 0.0)
+        limit, alpha, shift = self._gated(gated)
         rc = self.lib.somi_moe_gemv(
             _ptr(a), ctypes.c_longlong(a.stride(0)), ctypes.c_int(top if per_token else 1), _ptr(w),
             _ptr(token_ids), _ptr(table), ctypes.c_int(top), ctypes.c_int(E), ctypes.c_int(n),
             _ptr(out), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(1 if gated is not None else 0),
-            ctypes.c_float(limit), ctypes.c_float(alpha), self._stream())
+            ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(shift), self._stream())
         self._done(rc, "moe_gemv")
         if trace.active():
             trace.note("moe_gemv", (min(E, n) * N * K + n * K) * 2 + out.numel() * out.element_size(),
@@ -1002,6 +1017,225 @@ class CudaOps:
         if trace.active():
             trace.note("moe_combine", y.numel() * y.element_size()
                        + (out.numel() + (0 if extra is None else extra.numel())) * 4)
+        return out
+
+    # ------------------------------- side-by-side branches, matrix-state mixers, routers
+    def add_scaled_rmsnorm(self, residual, a, scale_a, b, scale_b, mult: float, extra, w1, w2,
+                           eps: float, out1, out2, rows=None) -> None:
+        """residual += mult * (scale_a * a + scale_b * b) + extra (float32, in place); then
+        out1 = rmsnorm(residual) * w1 and out2 = rmsnorm(residual) * w2 (each where given).
+        `a`, `b`: [N, H], or float32 [splits, N, H] partial sums added in order, or None; the
+        scales are [H] or None; `extra` float32 [N, H] or None.  With `rows`, only those rows are
+        produced and the residual is not written."""
+        _check(residual, a, scale_a, b, scale_b, extra, w1, w2, out1, out2, rows)
+        assert residual.dtype == torch.float32 and (extra is None or extra.dtype == torch.float32)
+        H = residual.shape[1]
+        n_out = residual.shape[0] if rows is None else rows.shape[0]
+
+        def parts(d):
+            if d is None:
+                return _F32, 1, 0
+            if d.dim() == 3:
+                assert d.dtype == torch.float32
+                return _F32, d.shape[0], d.shape[1] * d.shape[2]
+            return _code(d), 1, 0
+
+        (a_code, a_splits, a_stride), (b_code, b_splits, b_stride) = parts(a), parts(b)
+        scale = scale_a if scale_a is not None else scale_b
+        assert scale_a is None or scale_b is None or scale_a.dtype == scale_b.dtype
+        w = w1 if w1 is not None else w2
+        out = out1 if out1 is not None else out2
+        assert (w1 is None) == (out1 is None) and (w2 is None) == (out2 is None)
+        rc = self.lib.somi_add_scaled_rmsnorm(
+            _ptr(residual), _ptr(a), ctypes.c_int(a_code), ctypes.c_int(a_splits),
+            ctypes.c_longlong(a_stride), _ptr(scale_a), _ptr(b), ctypes.c_int(b_code),
+            ctypes.c_int(b_splits), ctypes.c_longlong(b_stride), _ptr(scale_b),
+            ctypes.c_int(_code(scale) if scale is not None else _F32), ctypes.c_float(mult),
+            _ptr(extra), _ptr(w1), _ptr(w2), ctypes.c_int(_code(w) if w is not None else _F32),
+            ctypes.c_float(eps), _ptr(out1), _ptr(out2),
+            ctypes.c_int(_code(out) if out is not None else _F32), _ptr(rows), ctypes.c_int(n_out),
+            ctypes.c_int(H), ctypes.c_int(0 if rows is not None else 1), self._stream())
+        self._done(rc, "add_scaled_rmsnorm")
+        if trace.active():
+            n = n_out * H
+            moved = n * 4 * (2 if rows is None else 1)
+            for d, splits in ((a, a_splits), (b, b_splits)):
+                if d is not None:
+                    moved += splits * n * d.element_size()
+            for o in (out1, out2):
+                if o is not None:
+                    moved += n * o.element_size()
+            if extra is not None:
+                moved += n * 4
+            trace.note("add_scaled_rmsnorm", moved)
+
+    def headnorm_rotary_store(self, qkv, positions, inv_freq, nq, nkv, hd, vd, rotary_dim, q_weight,
+                              k_weight, eps, slot_map, kcache, vcache) -> None:
+        """Rows of `qkv` hold nq query heads and nkv key heads of `hd` elements, then nkv value
+        heads of `vd`.  Every query and key head passes an RMS norm over the head with
+        `q_weight` / `k_weight` ([hd]; None: no norm); then entry i < rotary_dim / 2 and entry
+        i + rotary_dim / 2 turn by position * inv_freq[i] (`inv_freq` float64).  Queries are
+        rewritten in place; keys and values go to their cache slots (`slot_map` None: nothing is
+        stored)."""
+        _check(positions, inv_freq, slot_map, kcache, vcache, q_weight, k_weight)
+        if not (qkv.is_cuda and qkv.stride(1) == 1 and qkv.shape[1] >= (nq + nkv) * hd + nkv * vd):
+            raise KernelError("headnorm_rotary_store takes a device tensor with contiguous rows")
+        assert inv_freq.dtype == torch.float64 and inv_freq.numel() >= max(1, rotary_dim // 2)
+        assert (q_weight is None) == (k_weight is None)
+        page_size = 1
+        if slot_map is not None:
+            assert kcache.dtype == qkv.dtype and vcache.dtype == qkv.dtype
+            assert kcache.shape[1] == nkv and kcache.shape[3] == hd and vcache.shape[3] == vd
+            page_size = kcache.shape[2]
+        rc = self.lib.somi_headnorm_rotary_store(
+            _ptr(qkv), _code(qkv), ctypes.c_longlong(qkv.stride(0)), _ptr(positions), _ptr(inv_freq),
+            ctypes.c_int(qkv.shape[0]), ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd),
+            ctypes.c_int(vd), ctypes.c_int(rotary_dim), _ptr(q_weight), _ptr(k_weight),
+            ctypes.c_int(_code(q_weight) if q_weight is not None else _F32), ctypes.c_float(eps),
+            _ptr(slot_map), _ptr(kcache), _ptr(vcache), ctypes.c_int(page_size), self._stream())
+        self._done(rc, "headnorm_rotary_store")
+        if trace.active():
+            n = qkv.shape[0] * ((nq + nkv) * hd + nkv * vd)
+            trace.note("headnorm_rotary_store", 2 * n * qkv.element_size())
+
+    def check_matrix_state_geometry(self, heads: int, qk_heads: int, dk: int, dv: int) -> None:
+        most = int(self.lib.somi_matrix_state_scan_max_key())
+        if not (1 <= dk <= most and dv >= 1 and qk_heads >= 1 and heads % qk_heads == 0):
+            raise KernelError(f"a matrix-state mixer with {heads} heads over {qk_heads} query/key "
+                              f"heads of width {dk} is not supported (key width up to {most})")
+
+    def matrix_state_scan(self, q, k, v, state, batch, y, heads, qk_heads, dk, dv, *,
+                          act_silu=False, unit_eps=None, q_scale=1.0, beta=None, decay_logits=None,
+                          dt_bias=None, a_log=None, decay=None) -> None:
+        """Per request and head a float32 state S [dk, dv] in `state` [slots, heads, dk, dv],
+        continued over the request's rows of this step:
+            S <- g * S;  u = v, or with `beta` u = sigmoid(beta) * (v - S^T k);  S <- S + k u^T;
+            y = S^T q
+        g is `decay` [heads], or per key channel exp(-exp(a_log) * softplus(decay_logits +
+        dt_bias)) (`decay_logits` float32 [T, heads * dk], rows may lie further apart).  q, k
+        ([T, qk_heads * dk]) and v ([T, heads * dv]) may be views of wider rows; `act_silu`: they
+        pass SiLU as they are read; `unit_eps`: q and k are divided by sqrt(sum of squares + it)
+        and q is multiplied by `q_scale`.  y: float32 [T, heads * dv]."""
+        _check(state, y, dt_bias, a_log, decay)
+        for t in (q, k, v, beta, decay_logits):
+            if t is not None and not (t.is_cuda and t.stride(1) == 1):
+                raise KernelError("matrix_state_scan takes device tensors with contiguous rows")
+        assert q.dtype == k.dtype == v.dtype and (beta is None or beta.dtype == q.dtype)
+        assert state.dtype == y.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dk, dv)
+        assert decay_logits is None or decay_logits.dtype == torch.float32
+        for t in (dt_bias, a_log, decay):
+            assert t is None or t.dtype == torch.float32
+        rc = self.lib.somi_matrix_state_scan(
+            _ptr(q), _ptr(k), _ptr(v), _code(q), ctypes.c_longlong(q.stride(0)),
+            ctypes.c_longlong(k.stride(0)), ctypes.c_longlong(v.stride(0)),
+            ctypes.c_int(1 if act_silu else 0), ctypes.c_int(0 if unit_eps is None else 1),
+            ctypes.c_float(unit_eps or 0.0), ctypes.c_float(q_scale),
+            ctypes.c_int(0 if beta is None else 1), _ptr(beta),
+            ctypes.c_longlong(beta.stride(0) if beta is not None else 0), _ptr(decay_logits),
+            ctypes.c_longlong(decay_logits.stride(0) if decay_logits is not None else 0),
+            _ptr(dt_bias), _ptr(a_log), _ptr(decay), _ptr(state), _ptr(batch.cu_q),
+            _ptr(batch.state_slot), _ptr(y), ctypes.c_int(batch.num_requests), ctypes.c_int(heads),
+            ctypes.c_int(qk_heads), ctypes.c_int(dk), ctypes.c_int(dv), self._stream())
+        self._done(rc, "matrix_state_scan")
+        if trace.active():
+            T = q.shape[0]
+            moved = T * (2 * qk_heads * dk + heads * dv) * q.element_size() + T * heads * dv * 4 \
+                + 2 * batch.num_requests * heads * dk * dv * 4
+            if decay_logits is not None:
+                moved += T * heads * dk * 4
+            trace.note("matrix_state_scan", moved, (8.0 if beta is not None else 5.0) * T * heads * dk * dv,
+                       detail="delta rule" if beta is not None else "decayed sum")
+
+    def group_rmsnorm_gate(self, y, gate, weight, eps, groups, out) -> None:
+        """out = rmsnorm over each of `groups` equal parts of y (float32), times weight (as long
+        as a row, or as a part and then shared by the parts), times sigmoid(gate) where there is
+        a gate ([T, C], rows may lie further apart)."""
+        _check(y, weight, out)
+        if gate is not None and not (gate.is_cuda and gate.stride(1) == 1 and gate.shape == y.shape):
+            raise KernelError("group_rmsnorm_gate takes a gate with contiguous rows")
+        assert y.dtype == torch.float32
+        C = y.shape[1]
+        assert weight.numel() in (C, C // groups)
+        rc = self.lib.somi_group_rmsnorm_gate(
+            _ptr(y), _ptr(gate), ctypes.c_int(_code(gate) if gate is not None else _F32),
+            ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(weight), _code(weight),
+            ctypes.c_int(weight.numel()), ctypes.c_float(eps), _ptr(out), _code(out),
+            ctypes.c_int(y.shape[0]), ctypes.c_int(C), ctypes.c_int(groups), self._stream())
+        self._done(rc, "group_rmsnorm_gate")
+        if trace.active():
+            trace.note("group_rmsnorm_gate", y.numel() * (4 + out.element_size()
+                                                          + (gate.element_size() if gate is not None else 0)))
+
+    def rmsnorm_pair_mean(self, a, b, weight_a, weight_b, eps, out) -> None:
+        """out = (rmsnorm(a) * weight_a + rmsnorm(b) * weight_b) / 2, float32 [T, H].  `a`, `b`:
+        [T, H], or float32 [splits, T, H] partial sums that are added in order."""
+        _check(a, b, weight_a, weight_b, out)
+        assert out.dtype == torch.float32 and weight_a.dtype == weight_b.dtype
+        T, H = out.shape
+
+        def parts(d):
+            assert tuple(d.shape[-2:]) == (T, H)
+            if d.dim() == 3:
+                assert d.dtype == torch.float32
+                return _F32, d.shape[0], T * H
+            return _code(d), 1, 0
+
+        (a_code, a_splits, a_stride), (b_code, b_splits, b_stride) = parts(a), parts(b)
+        rc = self.lib.somi_rmsnorm_pair_mean(
+            _ptr(a), ctypes.c_int(a_code), ctypes.c_int(a_splits), ctypes.c_longlong(a_stride),
+            _ptr(b), ctypes.c_int(b_code), ctypes.c_int(b_splits), ctypes.c_longlong(b_stride),
+            _ptr(weight_a), _ptr(weight_b), _code(weight_a), ctypes.c_float(eps), _ptr(out),
+            ctypes.c_int(T), ctypes.c_int(H), self._stream())
+        self._done(rc, "rmsnorm_pair_mean")
+        if trace.active():
+            trace.note("rmsnorm_pair_mean", a.numel() * a.element_size() + b.numel() * b.element_size()
+                       + out.numel() * 4)
+
+    def relu2(self, x, out) -> None:
+        """out = max(x, 0)^2, elementwise."""
+        _check(x, out)
+        assert x.dtype == out.dtype and x.shape == out.shape
+        rc = self.lib.somi_relu2(_ptr(x), _ptr(out), _code(x), ctypes.c_longlong(x.numel()),
+                                 self._stream())
+        self._done(rc, "relu2")
+        if trace.active():
+            trace.note("relu2", 2 * x.numel() * x.element_size())
+
+    def moe_router_select(self, logits, correction, count: int, keep: int, top: int):
+        """logits float32 [T, n] -> (chosen int32 [T, top], weight float32 [T, top]): softmax over
+        the n outputs; the choice is made on softmax + correction (None: the softmax) among the
+        members of the `keep` best of `count` equal groups of neighbours (a group's score is its
+        best member's; count <= 1: no groups); the weights are the chosen outputs' softmax."""
+        _check(logits, correction)
+        assert logits.dtype == torch.float32 and (correction is None or correction.dtype == torch.float32)
+        T, n = logits.shape
+        chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+        weight = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+        rc = self.lib.somi_moe_router_select(_ptr(logits), ctypes.c_longlong(logits.stride(0)),
+                                             _ptr(correction), ctypes.c_int(T), ctypes.c_int(n),
+                                             ctypes.c_int(count), ctypes.c_int(keep), ctypes.c_int(top),
+                                             _ptr(chosen), _ptr(weight), self._stream())
+        self._done(rc, "moe_router_select")
+        if trace.active():
+            trace.note("moe_router_select", T * (n * 4 + top * 8))
+        return chosen, weight
+
+    def moe_combine_weighted(self, y, place, table, weight, x, num_experts: int) -> torch.Tensor:
+        """out[t] = sum_k weight[t, k] * (y[row(t * top + k)] if table[t, k] < num_experts else
+        x[t]); float32 [T, H].  `place`: the row of every entry where y's rows are in the grouped
+        order (None: row = entry)."""
+        _check(y, place, table, weight, x)
+        T, top = table.shape
+        H = x.shape[1]
+        assert y.shape[1] == H and weight.dtype == torch.float32 and table.dtype == torch.int32
+        out = torch.empty((T, H), dtype=torch.float32, device=x.device)
+        rc = self.lib.somi_moe_combine_weighted(_ptr(y), _code(y), _ptr(place), _ptr(table), _ptr(weight),
+                                                _ptr(x), _code(x), ctypes.c_int(num_experts),
+                                                ctypes.c_int(top), ctypes.c_int(T), ctypes.c_int(H),
+                                                _ptr(out), self._stream())
+        self._done(rc, "moe_combine_weighted")
+        if trace.active():
+            trace.note("moe_combine_weighted", T * top * H * y.element_size() + T * H * (4 + x.element_size()))
         return out
 
     def silu_mul(self, gu: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:

@@ -26,7 +26,8 @@ Interfaces (duck-typed; the classes below only document them):
                  part the layer does not have is None), with a fourth argument `extras`
                  (name -> built layer extra) where the layer has some; `forward(residual,
                  pending, batch, cache, owns_cache)` returns the delta that the next norm has to
-                 add (a tensor, or a `GatedDelta` / `NormedDelta` for norms that take one).  An arrangement
+                 add (a tensor, or a `GatedDelta` / `NormedDelta` / `ScaledBranches` for norms
+                 or arrangements that take one).  An arrangement
                  whose extras keep state per request answers `state_needs() -> StateNeeds`.
 * Layer extra:   whatever its arrangement calls; `declare(params)` and `__init__(params,
                  tensors, ctx)` like every part.
@@ -123,6 +124,32 @@ class NormedDelta:
     delta: torch.Tensor
     weight: torch.Tensor
     eps: float
+
+
+@dataclass
+class ScaledBranches:
+    """What a layer whose mixer and feed-forward read the same stream hands to the next norm: the
+    two results (each [T, H] or float32 [splits, T, H] partial sums; the second may be absent),
+    a per-channel scale for each (or None) and the factor of their sum.  The next norm adds
+    mult * (scale_a * a + scale_b * b) to the residual stream before it normalises.  `extra`:
+    float32 [T, H] rows that are added as well (see `with_extra_rows`)."""
+
+    a: torch.Tensor
+    scale_a: torch.Tensor | None
+    b: torch.Tensor | None
+    scale_b: torch.Tensor | None
+    mult: float
+    extra: torch.Tensor | None = None
+
+
+def with_extra_rows(pending, rows: torch.Tensor):
+    """`pending` with float32 rows [T, H] that the next norm adds to the residual stream as well
+    (a schedule that adds the embedding's output again in front of a run).  Only what a norm can
+    add in the same pass takes them."""
+    if isinstance(pending, ScaledBranches):
+        return ScaledBranches(pending.a, pending.scale_a, pending.b, pending.scale_b, pending.mult, rows)
+    raise ValueError("the layer in front of a run that adds the embedding's output again must "
+                     f"hand on its result as ScaledBranches, not {type(pending).__name__}")
 
 
 def names_of(params: Mapping[str, Any]) -> Mapping[str, str]:

@@ -9,7 +9,7 @@ while normalising, and returns its own feed-forward output as the next `pending`
 
 from __future__ import annotations
 
-from .base import GatedDelta, NormedDelta, StateNeeds
+from .base import GatedDelta, NormedDelta, ScaledBranches, StateNeeds
 from .registry import ARRANGEMENTS
 
 
@@ -118,3 +118,44 @@ class GatedPreNormBlock:
             return GatedDelta(y, gate)
         gate = self.feed_forward_gate.logits(h) if self.feed_forward_gate is not None else None
         return GatedDelta(self.feed_forward.forward(h, batch), gate)
+
+
+@ARRANGEMENTS.register("parallel_branches")
+class ParallelBranchesBlock:
+    """Mixer and feed-forward read the same stream, each through a norm of its own:
+        x = x + mult * (scale_m * mixer(norm_m(x)) + scale_f * feed_forward(norm_f(x)))
+    `scale_m`, `scale_f`: per-channel scales (layer extras `mixer_scale`, `feed_forward_scale`;
+    either may be absent), `mult` the factor of extra `branch_factor` (absent: 1).  A layer
+    without a feed-forward has the mixer's branch only.  Norms: `mixer`, and with a feed-forward
+    `feed_forward`; both must be RMS norms: one kernel adds what the layer before left (a
+    `ScaledBranches`), writes the stream and produces both normalised rows from it in float32."""
+
+    def __init__(self, mixer, feed_forward, norms, extras=None) -> None:
+        extras = dict(extras or {})
+        if mixer is None:
+            raise ValueError("the parallel-branches arrangement needs a mixer")
+        want = {"mixer"} | ({"feed_forward"} if feed_forward is not None else set())
+        if set(norms) != want:
+            raise ValueError(f"the parallel-branches arrangement takes the norms {sorted(want)}, "
+                             f"got {sorted(norms)}")
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = norms["mixer"]
+        self.feed_forward_norm = norms.get("feed_forward")
+        if self.feed_forward_norm is not None and self.feed_forward_norm.eps != self.mixer_norm.eps:
+            raise ValueError("the two norms of a parallel-branches layer share one eps")
+        scale_m = extras.pop("mixer_scale", None)
+        scale_f = extras.pop("feed_forward_scale", None)
+        factor = extras.pop("branch_factor", None)
+        if extras:
+            raise ValueError(f"the parallel-branches arrangement has no use for {sorted(extras)}")
+        self.mixer_scale = None if scale_m is None else scale_m.weight
+        self.feed_forward_scale = None if scale_f is None else scale_f.weight
+        self.mult = 1.0 if factor is None else factor.value
+
+    def forward(self, residual, pending, batch, cache, owns_cache):
+        hm, hf = self.mixer_norm.forward_pair(residual, pending, self.feed_forward_norm)
+        a = self.mixer.forward(hm, batch, cache, owns_cache)
+        f = None if self.feed_forward is None else self.feed_forward.forward(hf, batch)
+        return ScaledBranches(a, self.mixer_scale, f,
+                              None if f is None else self.feed_forward_scale, self.mult)

@@ -3,6 +3,9 @@
 * `sigmoid_gate`: logits = W h + b; the branch it gates is multiplied by sigmoid(logits) when
   the next norm adds it to the residual stream (the sigmoid and the product are float32, in the
   norm's kernel).
+* `channel_scale`: a per-channel factor of a residual branch (one weight per channel of the
+  model width); the arrangement hands it to the kernel that adds the branch.
+* `constant`: a number of the layer that its arrangement reads (`value`); it has no tensors.
 * `causal_taps`: h <- h + conv(h), a causal convolution over time on every channel,
   conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j) with zeros before a sequence's start.  The last
   taps - 1 inputs of every request are kept in a state slot, so a sequence may arrive in portions
@@ -66,3 +69,24 @@ class CausalTaps:
         out = torch.empty_like(h)
         self.ctx.ops.causal_taps(h, self.weight, state.get(self.STATE), batch, out)
         return out
+
+
+@LAYER_EXTRAS.register("channel_scale")
+class ChannelScale:
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        return [TensorDecl(names_of(params)["weight"], (int(params["size"]),), init="ones",
+                           matrix=False)]
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        self.weight = tensors[names_of(params)["weight"]]
+
+
+@LAYER_EXTRAS.register("constant")
+class Constant:
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        return []
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        self.value = float(params["value"])

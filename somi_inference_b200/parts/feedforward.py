@@ -54,7 +54,8 @@ class DenseFF:
 
     `activation` "xielu": with (p, q) the two numbers of the tensor `act`,
     act(z) = softplus(p) z^2 + z/2 for z > 0 and (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2
-    otherwise, evaluated in float32.  `forward(x, batch, side=...)` lets the caller ride a second
+    otherwise, evaluated in float32.  `activation` "relu2": act(z) = max(z, 0)^2; it has no tensor.
+    `forward(x, batch, side=...)` lets the caller ride a second
     projection of the same input (a gate of the residual branch) on the up projection's product:
     the side matrix's rows are appended to W_up's, and its output comes back as a view."""
 
@@ -64,8 +65,9 @@ class DenseFF:
     def declare(params) -> list[TensorDecl]:
         n = names_of(params)
         hidden, inter = int(params["hidden_size"]), int(params["intermediate_size"])
-        decl = [TensorDecl(n["up"], (inter, hidden)), TensorDecl(n["down"], (hidden, inter)),
-                TensorDecl(n["act"], (2,), matrix=False)]
+        decl = [TensorDecl(n["up"], (inter, hidden)), TensorDecl(n["down"], (hidden, inter))]
+        if params.get("activation") == "xielu":
+            decl.append(TensorDecl(n["act"], (2,), matrix=False))
         if params.get("bias"):
             decl += [TensorDecl(n["up_bias"], (inter,), init="zeros", matrix=False),
                      TensorDecl(n["down_bias"], (hidden,), init="zeros", matrix=False)]
@@ -73,8 +75,9 @@ class DenseFF:
 
     def __init__(self, params, tensors, ctx: BuildContext) -> None:
         n = names_of(params)
-        if params.get("activation") != "xielu":
-            raise ValueError(f"unknown activation {params.get('activation')!r} (known: 'xielu')")
+        self.activation = params.get("activation")
+        if self.activation not in ("xielu", "relu2"):
+            raise ValueError(f"unknown activation {self.activation!r} (known: 'xielu', 'relu2')")
         self.ctx = ctx
         self.inter = int(params["intermediate_size"])
         bias = bool(params.get("bias"))
@@ -83,7 +86,7 @@ class DenseFF:
         self.up = Linear(self.up_weight, self.up_bias, ctx.ops)
         self.down = Linear(tensors[n["down"]], tensors[n["down_bias"]].float() if bias else None,
                            ctx.ops)
-        self.act = tensors[n["act"]].float().contiguous()
+        self.act = tensors[n["act"]].float().contiguous() if self.activation == "xielu" else None
         self._with_side = None
 
     def attach_side(self, weight: torch.Tensor, bias: torch.Tensor | None) -> None:
@@ -98,13 +101,20 @@ class DenseFF:
 
     def forward(self, x: torch.Tensor, batch, side: bool = False):
         proj = self._with_side if side else self.up
-        fused = proj.xielu_side(x, self.act, self.inter)      # few tokens: in the product's epilogue
+        fused = None
+        if self.activation == "xielu":
+            fused = proj.xielu_side(x, self.act, self.inter)  # few tokens: in the product's epilogue
         if fused is not None:
             act, rest = fused
         else:
             z = proj(x)                                 # [T, inter (+ side)]
             act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-            self.ctx.ops.xielu(z, self.inter, self.act, act)
+            if self.activation == "xielu":
+                self.ctx.ops.xielu(z, self.inter, self.act, act)
+            elif z.shape[1] == self.inter:
+                self.ctx.ops.relu2(z, act)
+            else:
+                self.ctx.ops.relu2(z[:, :self.inter].contiguous(), act)
             rest = z[:, self.inter:]
         partial = self.down.partial_sums(act)
         y = partial if partial is not None else self.down(act)

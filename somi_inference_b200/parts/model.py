@@ -13,7 +13,7 @@ from __future__ import annotations
 import torch
 
 from ..config.spec import LayerSpec, ModelSpec
-from .base import BuildContext, CacheNeeds, StateNeeds, TensorDecl
+from .base import BuildContext, CacheNeeds, StateNeeds, TensorDecl, with_extra_rows
 from .registry import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, LAYER_EXTRAS, MIXERS,
                        NORMS)
 
@@ -99,7 +99,12 @@ class Decoder:
         """Run the step's tokens; return float32 logits [len(batch.logit_rows), vocab]."""
         residual = self.embedding.forward(batch)
         pending = None
+        # a schedule that adds the embedding's output again keeps a copy of it: the stream itself
+        # is written by the norms from the first run on
+        start = residual.clone() if any(run.add_embedding for run in self.schedule) else None
         for i, run in enumerate(self.schedule):
+            if run.add_embedding:
+                pending = with_extra_rows(pending, start)
             pending = self.layers[run.layer].forward(residual, pending, batch, cache.view(i),
                                                      run.cache_of is None)
         if batch.logit_rows.shape[0] == 0:

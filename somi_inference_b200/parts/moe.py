@@ -1,4 +1,6 @@
-"""Mixture of experts routed by a table: a token's id names its experts.
+"""Mixtures of experts: routed by a table (`table_moe`) or by a router (`routed_moe`, at the end).
+
+`table_moe`: a token's id names its experts.
 
     experts of token t: table[id_t, 0..top-1] (distinct), each weighted 1 / top
     expert(h) = W_down (g * sigmoid(alpha * g) * (u + 1)),
@@ -98,3 +100,82 @@ class TableMoE:
         act = ops.grouped_product(x, self.w_gate_up, route=route, top=top, gather=True, gated=self.gated)
         y = ops.grouped_product(act, self.w_down, route=route, top=top, scatter=True, out_float32=True)
         return ops.moe_combine(y, extra, 1.0 / top, top)
+
+
+@FEED_FORWARDS.register("routed_moe")
+class RoutedMoE:
+    """A mixture of experts whose router is a product over the token:
+
+        s = softmax(W_router h) over all n = experts + identity outputs           (float32)
+        choice = s + correction                  (a stored vector; it decides, it does not weigh)
+        the n outputs form `groups.count` equal groups of neighbours; a group's score is its best
+        choice; only members of the `groups.keep` best groups can be chosen
+        the `top` best choices are the token's experts, each weighted by its s (not renormalised)
+        expert(h) = W_down (silu(W_gate h) * (W_up h)); the last `identity` outputs are identity
+        experts without tensors: expert(h) = h
+        y = sum of weight * expert(h) over the chosen
+
+    The router's logits are a float32 product; one kernel makes softmax, choice and weights and
+    leaves a table row per token, from which the experts run like those of `table_moe`: entry by
+    entry for a step of few tokens, grouped by expert otherwise.  The weighted sum is float32."""
+
+    graph_safe = True
+
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        n = names_of(params)
+        hidden, E = int(params["hidden_size"]), int(params["experts"])
+        ff, outputs = int(params["expert_ff"]), E + int(params.get("identity", 0))
+        decl = [TensorDecl(n["router"], (outputs, hidden))]
+        if params.get("correction"):
+            decl.append(TensorDecl(n["correction"], (outputs,), init="zeros", matrix=False))
+        for e in range(E):
+            decl += [TensorDecl(n["gate"][e], (ff, hidden)), TensorDecl(n["up"][e], (ff, hidden)),
+                     TensorDecl(n["down"][e], (hidden, ff))]
+        return decl
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        n = names_of(params)
+        self.ctx = ctx
+        self.experts, self.top = int(params["experts"]), int(params["top"])
+        self.outputs = self.experts + int(params.get("identity", 0))
+        groups = params.get("groups") or {}
+        self.group_count = int(groups.get("count", 1))
+        self.group_keep = int(groups.get("keep", self.group_count))
+        if self.experts < 1 or not 1 <= self.top <= self.outputs:
+            raise ValueError(f"top = {self.top} of {self.outputs} router outputs")
+        if self.outputs % self.group_count or not 1 <= self.group_keep <= self.group_count:
+            raise ValueError(f"{self.outputs} router outputs in {self.group_count} groups, of which "
+                             f"{self.group_keep} are kept")
+        if self.top > self.group_keep * (self.outputs // self.group_count):
+            raise ValueError("the kept groups hold fewer outputs than a token chooses")
+        self.router = Linear(tensors[n["router"]], None, ctx.ops)
+        self.correction = (tensors[n["correction"]].float().contiguous()
+                           if params.get("correction") else None)
+        E = range(self.experts)
+        self.w_gate_up = _interleave(torch.stack([tensors[n["gate"][e]] for e in E]),
+                                     torch.stack([tensors[n["up"][e]] for e in E])).contiguous()
+        self.w_down = torch.stack([tensors[n["down"][e]] for e in E]).contiguous()
+        self.gated = (float("inf"), 1.0, 0.0)               # silu(gate) * up
+
+    def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
+        ops, top, E = self.ctx.ops, self.top, self.experts
+        logits = self.router.to_float32(x)
+        chosen, weight = ops.moe_router_select(logits, self.correction, self.group_count,
+                                               self.group_keep, top)
+        n_entries = x.shape[0] * top
+        if ops.moe_gemv_supported(n_entries, x.shape[1], x.dtype) and self.w_down.shape[2] % 8 == 0:
+            act = ops.moe_gemv(x, self.w_gate_up, None, chosen, per_token=True, gated=self.gated)
+            y = ops.moe_gemv(act, self.w_down, None, chosen, per_token=False)
+            return ops.moe_combine_weighted(y, None, chosen, weight, x, E)
+        route = ops.moe_route(None, chosen, E, self.outputs)
+        if x.dtype == torch.bfloat16:
+            rows = ops.moe_gather_rows(x, route, E, top)
+            gu = ops.library_grouped_product(rows, self.w_gate_up, route)
+            if gu is not None:
+                y = ops.library_grouped_product(ops.clamped_gate_up(gu, *self.gated), self.w_down, route)
+                if y is not None:
+                    return ops.moe_combine_weighted(y, ops._route_parts(route, E)[2], chosen, weight, x, E)
+        act = ops.grouped_product(x, self.w_gate_up, route=route, top=top, gather=True, gated=self.gated)
+        y = ops.grouped_product(act, self.w_down, route=route, top=top, scatter=True, out_float32=True)
+        return ops.moe_combine_weighted(y, None, chosen, weight, x, E)

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import BuildContext, GatedDelta, NormedDelta, TensorDecl, names_of
+from .base import BuildContext, GatedDelta, NormedDelta, ScaledBranches, TensorDecl, names_of
 from .registry import NORMS
 
 
@@ -33,12 +33,38 @@ class RMSNorm:
         `NormedDelta`: the branch's result passes an RMS norm of its own before it is added."""
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=residual.device)
-        if isinstance(delta, NormedDelta):
+        if isinstance(delta, ScaledBranches):
+            self.ctx.ops.add_scaled_rmsnorm(residual, delta.a, delta.scale_a, delta.b, delta.scale_b,
+                                            delta.mult, delta.extra, self.weight, None, self.eps,
+                                            out, None, rows)
+        elif isinstance(delta, NormedDelta):
             self.ctx.ops.add_normed_rmsnorm(residual, delta.delta, delta.weight, delta.eps,
                                             self.weight, self.eps, out, rows)
         else:
             self.ctx.ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows)
         return out
+
+    def forward_pair(self, residual: torch.Tensor, delta, other: "RMSNorm | None"):
+        """Add `delta` (a `ScaledBranches`, a tensor, partial sums or None) to the residual
+        stream and normalise it twice, with this norm's weight and with `other`'s (None: once),
+        in one pass over the rows.  Returns the two results (the second None without `other`)."""
+        if delta is not None and not isinstance(delta, ScaledBranches):
+            if isinstance(delta, (NormedDelta, GatedDelta)):
+                raise ValueError("a layer of parallel branches cannot follow one whose result "
+                                 "passes a norm or a gate of its own")
+            delta = ScaledBranches(delta, None, None, None, 1.0)
+        if other is not None and other.weight.dtype != self.weight.dtype:
+            raise ValueError("the two norms of a layer hold their weights in one precision")
+        shape = (residual.shape[0], self.size)
+        out1 = torch.empty(shape, dtype=self.ctx.dtype, device=residual.device)
+        out2 = None if other is None else torch.empty(shape, dtype=self.ctx.dtype, device=residual.device)
+        d = delta
+        self.ctx.ops.add_scaled_rmsnorm(
+            residual, None if d is None else d.a, None if d is None else d.scale_a,
+            None if d is None else d.b, None if d is None else d.scale_b,
+            1.0 if d is None else d.mult, None if d is None else d.extra, self.weight,
+            None if other is None else other.weight, self.eps, out1, out2, None)
+        return out1, out2
 
 
 @NORMS.register("layernorm")

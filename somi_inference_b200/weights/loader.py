@@ -57,6 +57,14 @@ def _open_files(model_dir: str) -> dict[str, SafetensorsFile]:
                             "model.safetensors.index.json")
 
 
+def tensor_shapes(model_dir: str) -> dict[str, tuple[int, ...]]:
+    """name -> shape of every tensor in the folder's weight file(s); only the headers are read.
+    An architecture whose config.json leaves a size to the tensors (`with_shapes` of its config
+    class) gets it from here."""
+    files = _open_files(model_dir)
+    return {name: tuple(f.info(name)[1]) for name, f in files.items()}
+
+
 def load_tensors(model_dir: str, declared: Mapping[str, TensorDecl],
                  optional: tuple[str, ...] = ()) -> dict[str, torch.Tensor]:
     """Return {name: CPU tensor in its stored dtype} for every declared tensor that is read.
