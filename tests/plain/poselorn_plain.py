@@ -178,29 +178,77 @@ def dense_ff(h, w, prefix):
     return (z * z) @ w[p + "down"].T + w[p + "down.b"]
 
 
+def choose_experts(z, correction, groups, top):
+    """z [S, n] router logits -> (chosen [S, top], weights [S, top]).  s = softmax(z); the choice
+    is made on s + correction; with `groups` = (count, keep) the n outputs are cut into `count`
+    equal runs of neighbours, a run's score is its largest choice, and outputs outside the `keep`
+    best runs cannot be chosen; the weights are the chosen outputs' s."""
+    s = torch.softmax(z, dim=-1)
+    choice = s + correction
+    if groups:
+        count, keep = groups
+        size = z.shape[-1] // count
+        best = choice.reshape(-1, count, size).max(dim=-1).values
+        kept = best.topk(keep, dim=-1).indices
+        allowed = torch.zeros_like(best, dtype=torch.bool).scatter_(1, kept, True)
+        choice = torch.where(allowed.repeat_interleave(size, dim=1), choice,
+                             torch.full_like(choice, -math.inf))
+    chosen = choice.topk(top, dim=-1).indices
+    return chosen, s.gather(1, chosen)
+
+
+def choice_margin(z, correction, groups, top, least_weight: float = 0.0):
+    """How far a token's choice is from another one [S]: the smallest distance between two choice
+    scores where the order of the two decides who is chosen (the last chosen output against the
+    best one left out, and with groups the last kept group against the best one dropped).
+    Infinite where there is nothing to decide, or where neither side of the decision holds an
+    output whose weight s exceeds `least_weight` (the other choice would change next to nothing)."""
+    s = torch.softmax(z, dim=-1)
+    choice = s + correction
+    inf = torch.full((z.shape[0],), math.inf, dtype=z.dtype)
+    margin = inf
+    if groups:
+        count, keep = groups
+        size = z.shape[-1] // count
+        best = choice.reshape(-1, count, size).max(dim=-1).values
+        order = best.sort(dim=-1, descending=True)
+        if keep < count:
+            heaviest = s.reshape(-1, count, size).max(dim=-1).values
+            stake = torch.maximum(heaviest.gather(1, order.indices[:, keep - 1:keep]),
+                                  heaviest.gather(1, order.indices[:, keep:keep + 1]))[:, 0]
+            margin = torch.where(stake > least_weight, order.values[:, keep - 1] - order.values[:, keep], inf)
+        allowed = torch.zeros_like(best, dtype=torch.bool).scatter_(1, order.indices[:, :keep], True)
+        choice = torch.where(allowed.repeat_interleave(size, dim=1), choice,
+                             torch.full_like(choice, -math.inf))
+    if top < z.shape[-1]:
+        order = choice.sort(dim=-1, descending=True)
+        gap = order.values[:, top - 1] - order.values[:, top]
+        stake = torch.maximum(s.gather(1, order.indices[:, top - 1:top]),
+                              s.gather(1, order.indices[:, top:top + 1]))[:, 0]
+        gap = torch.where(torch.isfinite(gap) & (stake > least_weight), gap, inf)
+        margin = torch.minimum(margin, gap)
+    return margin
+
+
 def route(h, w, prefix, mlp):
     """-> (chosen [S, top] indices into experts + identity experts, their weights [S, top])."""
     p = prefix + ".mlp."
     r = mlp["router"]
-    n = r["experts"] + r.get("identity", 0)
-    s = torch.softmax(h @ w[p + "router"].T, dim=-1)
-    choice = s + w[p + "correction"]
     groups = r.get("groups")
-    if groups:
-        size = n // groups["count"]
-        best = choice.reshape(-1, groups["count"], size).max(dim=-1).values
-        kept = best.topk(groups["keep"], dim=-1).indices
-        allowed = torch.zeros_like(best, dtype=torch.bool).scatter_(1, kept, True)
-        choice = torch.where(allowed.repeat_interleave(size, dim=1), choice,
-                             torch.full_like(choice, -math.inf))
-    chosen = choice.topk(r["top"], dim=-1).indices
-    return chosen, s.gather(1, chosen)
+    return choose_experts(h @ w[p + "router"].T, w[p + "correction"],
+                          (groups["count"], groups["keep"]) if groups else None, r["top"])
 
 
-def moe_ff(h, w, prefix, mlp):
+def moe_ff(h, w, prefix, mlp, margins: list | None = None, least_weight: float = 0.02):
     p = prefix + ".mlp."
     E = mlp["router"]["experts"]
     chosen, weight = route(h, w, prefix, mlp)
+    if margins is not None:
+        r = mlp["router"]
+        groups = r.get("groups")
+        margins.append(choice_margin(h @ w[p + "router"].T, w[p + "correction"],
+                                     (groups["count"], groups["keep"]) if groups else None, r["top"],
+                                     least_weight))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, c in zip(chosen[t].tolist(), weight[t]):
@@ -226,7 +274,7 @@ def layer_order(cfg):
     return runs + [(i, False) for i in range(loop["stop"], n)]
 
 
-def layer(x, w, i, lc, cfg):
+def layer(x, w, i, lc, cfg, margins: list | None = None):
     eps, mult = cfg["norm"]["eps"], cfg["residual_mult"]
     p = f"l{i}"
     h = rms_norm(x, w[p + ".norm1"], eps)
@@ -238,20 +286,30 @@ def layer(x, w, i, lc, cfg):
     mlp = lc.get("mlp")
     if mlp:
         h2 = rms_norm(x, w[p + ".norm2"], eps)
-        f = dense_ff(h2, w, p) if mlp["kind"] == "dense" else moe_ff(h2, w, p, mlp)
+        f = dense_ff(h2, w, p) if mlp["kind"] == "dense" else moe_ff(h2, w, p, mlp, margins)
         total = total + f * w[p + ".ls2"]
     return x + mult * total
 
 
-def forward(cfg, w, tokens, dtype=torch.float64, residuals: list | None = None):
-    """Logits [S, vocab] of one sequence; `residuals` collects x after every layer run."""
+def forward(cfg, w, tokens, dtype=torch.float64, residuals: list | None = None,
+            margins: list | None = None):
+    """Logits [S, vocab] of one sequence; `residuals` collects x after every layer run, `margins`
+    one tensor [S] per routed feed-forward that ran (see `choice_margin`)."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     start = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * cfg["embedding"]["scale"]
     x = start
     for i, again in layer_order(cfg):
         if again:
             x = x + start
-        x = layer(x, w, i, cfg["layers"][i], cfg)
+        x = layer(x, w, i, cfg["layers"][i], cfg, margins)
         if residuals is not None:
             residuals.append(x)
     return rms_norm(x, w["final.norm"], cfg["norm"]["eps"]) @ w["head"].T
+
+
+def greedy(cfg: dict, weights: dict, prompt, n_new: int, dtype=torch.float64) -> list[int]:
+    """Greedy continuation by recomputing the whole sequence for every new token."""
+    seq = list(prompt)
+    for _ in range(n_new):
+        seq.append(int(forward(cfg, weights, seq, dtype)[-1].argmax()))
+    return seq[len(prompt):]

@@ -8,11 +8,10 @@ requests; convolutions start inside a request's history and at its very beginnin
 import pytest
 import torch
 
-from somi_inference_b200.cache import CacheManager
 from somi_inference_b200.config.spec import PartSpec
-from somi_inference_b200.engine.batch import BatchBuilder, StepEntry
 from somi_inference_b200.parts import FEED_FORWARDS, BuildContext
-from somi_inference_b200.parts.base import CacheNeeds, PagedKVNeeds, StateNeeds
+from somi_inference_b200.parts.base import PagedKVNeeds, StateNeeds
+from tests.gpu_util import Steps, gather_cache
 from tests.plain import dapozen_plain as plain
 
 pytestmark = pytest.mark.gpu
@@ -28,43 +27,6 @@ def ops():
 
 def tol(dtype, f32=2e-5, bf16=2e-2):
     return f32 if dtype == torch.float32 else bf16
-
-
-class Steps:
-    """A cache manager and batch builder that are fed several steps of the same requests."""
-
-    def __init__(self, ops, n_requests, *, paged=None, state=None, page_size=8, max_len=512,
-                 dtype=torch.float32, seed=0, num_pages=None):
-        g = torch.Generator().manual_seed(seed)
-        needs = CacheNeeds(paged=paged or PagedKVNeeds(1, 8, None, value_dim=0), state=state)
-        pages = num_pages or n_requests * (-(-max_len // page_size)) + 3
-        self.mgr = CacheManager([needs], [None], num_pages=pages, page_size=page_size,
-                                max_requests=n_requests, max_positions=max_len + page_size,
-                                dtype=dtype, device="cuda")
-        pool = self.mgr.groups[0].pool
-        taken = pool.take(pool.num_free)
-        pool.give_back([taken[i] for i in torch.randperm(len(taken), generator=g).tolist()])
-        self.builder = BatchBuilder(self.mgr, device="cuda", q_tile_sizes=ops.q_tile_sizes)
-        self.pending = []
-
-    def step(self, counts: dict):
-        """`counts`: request -> tokens in this step.  Returns (batch, {request: (first row, rows,
-        tokens cached before)})."""
-        for r in self.pending:
-            self.mgr.commit(r)
-        entries = []
-        for r, q in counts.items():
-            if not self.mgr.is_registered(r):
-                self.mgr.register(r)
-            self.mgr.reserve(r, q)
-            entries.append(StepEntry(r, [0] * q, []))
-        self.pending = list(counts)
-        batch, _ = self.builder.build(entries)
-        where = {}
-        for j, r in enumerate(batch.host.requests):
-            first = int(batch.host.cu_q[j])
-            where[r] = (first, int(batch.host.cu_q[j + 1]) - first, int(batch.host.ctx_len[j]))
-        return batch, where
 
 
 # ------------------------------------------------------------------ embedding, norms, cap
@@ -198,17 +160,6 @@ def test_rotary_pairs_store(ops, dtype, geometry):
 
 
 # ------------------------------------------------------------------ chunked attention
-def gather_cache(view, table_row, length, page_size):
-    keys = torch.zeros((length, view.keys.shape[1], view.keys.shape[3]), dtype=torch.float64)
-    values = torch.zeros((length, view.values.shape[1], view.values.shape[3]), dtype=torch.float64)
-    for p in range(length):
-        page = int(table_row[p // page_size])
-        if page >= 0:
-            keys[p] = view.keys[page, :, p % page_size].double().cpu()
-            values[p] = view.values[page, :, p % page_size].double().cpu()
-    return keys, values
-
-
 @pytest.mark.parametrize("case", [
     # (heads, kv heads, key width, value width, chunk, page size)
     (4, 2, 12, 20, 9, 8), (2, 1, 16, 16, 21, 4), (3, 3, 5, 3, 1, 4), (2, 2, 32, 8, 64, 16),
