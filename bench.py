@@ -6,6 +6,7 @@
                     [--context C] [--prefill-tokens T] [--profile]      one phase (profiling runs)
     python bench.py --arch digosun --only decode|prefill [...]   the same shapes with Digosun layers
     python bench.py --arch dapozen --only decode|prefill [...]   the same shapes with Dapozen layers
+    python bench.py --arch poselorn --only decode|prefill [...]  the same shapes with Poselorn layers
 
 A step is one decode step of the whole engine: 8 requests with 2,048 cached tokens each,
 random bfloat16 weights, one new token per request (batch layout upload, all layers, head,
@@ -23,6 +24,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import platform
 import subprocess
@@ -64,6 +66,14 @@ DIGOSUN_TAPS = 4
 # the model's, heads of 64, a state of 128 and four groups; sixteen experts of a quarter of the
 # dense feed-forward's width, two per token, and a shared expert of the same width.
 DAPOZEN = dict(chunk=8192, taps=4, ssm_head=64, ssm_state=128, ssm_groups=4, experts=16, top=2)
+# `--arch poselorn`: the same widths, head counts, head sizes and vocabularies with Poselorn layers
+# in the pattern delta rule + dense, window attention beside a decayed sum + experts (twice), delta
+# rule + experts.  The delta rule has the shape's heads over half as many query/key heads, four
+# taps and narrow decay and gate projections; the window is longer than the timed contexts (the
+# attention reads what the Qwen2 layer reads); the decayed sum has the shape's heads at the same
+# widths; sixteen experts of a quarter of the dense feed-forward's width and four identity experts
+# in four groups of which three are kept, three per token.
+POSELORN = dict(window=8192, taps=4, rank=128, experts=16, identity=4, top=3, groups=(4, 3))
 CONTEXT = 2048          # cached tokens per request when decode is timed
 MAX_CONTEXT = 4096      # "benchmark at context 4096": positions the model is laid out for
 LONG_CONTEXT = 40960    # ... when the points at 8 k and 32 k cached tokens are measured too
@@ -237,19 +247,43 @@ def dapozen_config(shape: str, layers: int, positions: int) -> dict:
             "layers": [dict(zip(("type", "mixer", "mlp"), pattern[i % 4])) for i in range(layers)]}
 
 
-ARCH = "qwen2"     # set by --arch; "digosun" / "dapozen" build the same shapes with their layers
+def poselorn_config(shape: str, layers: int, positions: int) -> dict:
+    q, z = SHAPES[shape], POSELORN
+    D, hd, H = q["hidden_size"], q["head_dim"], q["num_attention_heads"]
+    delta = dict(heads=H, kv_heads=H // 2, dim=hd, vdim=hd, conv=z["taps"], decay_rank=z["rank"],
+                 gate_rank=z["rank"])
+    left = dict(heads=H, kv_heads=q["num_key_value_heads"], dim=hd, vdim=hd, scale=hd ** -0.5,
+                rot={"dims": hd, "base": q["rope_theta"]}, mask={"size": z["window"]})
+    right = dict(heads=H, dim=hd, vdim=hd,
+                 decay=[math.exp(-2.0 ** -(1.0 + 7.0 * h / max(1, H - 1))) for h in range(H)])
+    both = {"left": left, "right": right}
+    dense = {"kind": "dense", "ff": q["intermediate_size"]}
+    moe = {"kind": "moe", "expert": {"ff": q["intermediate_size"] // 4},
+           "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"],
+                      "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
+    pattern = [("channel_delta", delta, dense), ("parallel", both, moe), ("parallel", both, moe),
+               ("channel_delta", delta, moe)]
+    return {"architecture": "Poselorn", "vocab": q["vocab_size"], "width": D,
+            "norm": {"eps": q["rms_norm_eps"]}, "embedding": {"scale": 1.0}, "residual_mult": 0.5,
+            "max_positions": positions,
+            "layers": [dict(zip(("type", "mixer", "mlp"), pattern[i % 4])) for i in range(layers)]}
+
+
+ARCH = "qwen2"     # set by --arch; the other architectures build the same shapes with their layers
 
 
 def build_engine(shape: str, layers: int, max_tokens: int, max_requests: int, positions: int):
     import torch
 
-    from somi_inference_b200.config import DapozenConfig, DigosunConfig, Qwen2Config
+    from somi_inference_b200.config import DapozenConfig, DigosunConfig, PoselornConfig, Qwen2Config
     from somi_inference_b200.engine import Engine
     from somi_inference_b200.parts import declared_tensors
     if ARCH == "digosun":
         cfg = DigosunConfig.from_dict(digosun_config(shape, layers, positions))
     elif ARCH == "dapozen":
         cfg = DapozenConfig.from_dict(dapozen_config(shape, layers, positions))
+    elif ARCH == "poselorn":
+        cfg = PoselornConfig.from_dict(poselorn_config(shape, layers, positions))
     else:
         cfg = Qwen2Config.from_dict(shape_config(shape, layers, positions))
     gen = torch.Generator(device="cuda").manual_seed(0)
@@ -343,9 +377,61 @@ def dapozen_sizes(cfg, batch: int) -> dict:
                            else 1 << 30) for l in cfg.layers)}
 
 
+def poselorn_sizes(cfg, batch: int) -> dict:
+    """The same figures for a Poselorn model.  A decode step of `batch` tokens reads at most
+    batch * top experts of a layer (identity experts have no weights); every matrix state is read
+    and written once per request and step in float32; the recurrences' flops (8 per state entry
+    and token for the delta rule, 5 for the decayed sum) are counted with the products."""
+    D, V = cfg.width, cfg.vocab
+    params = read_params = small = kv = pair = state = 0
+    for i, _ in cfg.runs():
+        layer = cfg.layers[i]
+        m = layer.mixer
+        if layer.type == "channel_delta":
+            qk, v = m["kv_heads"] * m["dim"], m["heads"] * m["vdim"]
+            ra, rg = m.get("decay_rank", 16), m.get("gate_rank", 16)
+            p = (2 * qk + v) * D + (ra + rg + m["heads"]) * D + m["heads"] * m["dim"] * ra + v * rg + D * v
+            p += 4 * m["heads"] * m["dim"] * m["vdim"]
+            small += (2 * qk + v) * m["conv"] + m["heads"] * m["dim"] + m["heads"] + m["vdim"]
+            state += 2 * 4 * m["heads"] * m["dim"] * m["vdim"]
+        else:
+            a, b = m["left"], m["right"]
+            qkv = (a["heads"] + a["kv_heads"]) * a["dim"] + a["kv_heads"] * a["vdim"]
+            p = qkv * D + D * a["heads"] * a["vdim"]
+            p += (2 * b["heads"] * b["dim"] + 2 * b["heads"] * b["vdim"]) * D + D * b["heads"] * b["vdim"]
+            p += 5 * b["heads"] * b["dim"] * b["vdim"] // 2
+            small += qkv + 2 * a["dim"] + b["heads"] * b["vdim"] + 2 * D
+            kv += 2 * a["kv_heads"] * (a["dim"] + a["vdim"])
+            pair += 2 * a["heads"] * (a["dim"] + a["vdim"])
+            state += 2 * 4 * b["heads"] * b["dim"] * b["vdim"]
+        params += p
+        read_params += p
+        small += 4 * D
+        mlp = layer.mlp
+        if mlp is None:
+            continue
+        if mlp["kind"] == "dense":
+            params += 2 * D * mlp["ff"]
+            read_params += 2 * D * mlp["ff"]
+            small += mlp["ff"] + D
+        else:
+            r = mlp["router"]
+            one = 3 * D * mlp["expert"]["ff"]
+            outputs = r["experts"] + r.get("identity", 0)
+            params += r["top"] * one * r["experts"] // outputs + outputs * D
+            read_params += min(r["experts"], batch * r["top"]) * one + outputs * D
+    windows = [l.mixer["left"]["mask"]["size"] if l.type == "parallel" and l.mixer["left"].get("mask")
+               else 1 << 30 for l in cfg.layers]
+    return {"weight_bytes": 2 * (read_params + small + V * D + D), "kv_bytes_per_token": kv,
+            "matmul_params": params, "head_params": V * D, "attn_flops_per_pair": pair,
+            "state_bytes_per_request": state, "window": min(windows)}
+
+
 def model_sizes(cfg, layers: int, batch: int = 1) -> dict:
     if ARCH == "digosun":
         return digosun_sizes(cfg)
+    if ARCH == "poselorn":
+        return poselorn_sizes(cfg, batch)
     if ARCH == "dapozen":
         return dapozen_sizes(cfg, batch)
     H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
@@ -939,7 +1025,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--shape", choices=list(SHAPES), default="7b")
-    ap.add_argument("--arch", choices=["qwen2", "digosun", "dapozen"], default="qwen2",
+    ap.add_argument("--arch", choices=["qwen2", "digosun", "dapozen", "poselorn"], default="qwen2",
                     help="with --only decode|prefill: the layer design the shape is built with "
                          "(digosun: latent attention under a window, gated branches; dapozen: "
                          "chunked attention with convolutions, Mamba-2 layers, table-routed experts)")
