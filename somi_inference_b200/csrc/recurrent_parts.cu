@@ -214,17 +214,49 @@ __global__ void headnorm_rotary_store_kernel(T* __restrict__ qkv, long long stri
 // pass SiLU as they are read; with `unit` q and k are divided by sqrt(sum of squares + unit_eps)
 // and q is multiplied by q_scale.
 // A CTA owns kRecCols columns of S for one (request, head) and walks through the request's rows
-// of this step, kRecBlock rows staged in shared memory at a time.  A column is held by 8 lanes,
-// lane l the rows l + 8 i; the sums over rows are taken in a fixed order (i ascending in a lane,
-// then a butterfly over the 8 lanes), so y does not depend on how the rows were cut into steps.
+// of this step, kRecBlock rows at a time.  Four warps hold the state: a column is held by 8 lanes,
+// each lane runs of four neighbouring rows; the sums over rows are taken in a fixed order (four
+// partial sums per lane, each ascending, added in pairs, then a butterfly over the 8 lanes), so y
+// does not depend on how the rows were cut into steps.  Four more warps stage the next block meanwhile: they read q, k,
+// the decay logits, v and beta of its rows, apply the activations, the unit norms and the decay's
+// exponentials (a warp per row) and leave float32 values in the other of two shared buffers.
 constexpr int kRecLanes = 8;
 constexpr int kRecWarps = 4;
+constexpr int kRecLoaders = 4;
 constexpr int kRecColsPerWarp = 32 / kRecLanes;
 constexpr int kRecCols = kRecWarps * kRecColsPerWarp;
-constexpr int kRecBlock = 8;
-constexpr int kRecThreads = kRecWarps * 32;
+constexpr int kRecBlockLong = 16;                        // rows staged at a time in a long step
+constexpr int kRecBlockShort = 4;                        // and in a step of few rows per request
+constexpr int kRecThreads = (kRecWarps + kRecLoaders) * 32;
 
-template <typename T, int R, bool DELTA>
+// floats of one staged block of B rows: q, k, g [B][DP], v [B][kRecCols], beta [B]
+__host__ __device__ constexpr int rec_buffer_floats(int B, int DP) {
+    return B * (3 * DP + kRecCols + 1);
+}
+
+// A state lane `sub` of 8 holds R rows in runs of V neighbours: entry i is row
+// 8 V (i / V) + V sub + i % V, so that the 8 lanes read 8 V neighbouring floats with one load each.
+template <int V>
+__device__ __forceinline__ int rec_row(int sub, int i) {
+    return kRecLanes * V * (i / V) + V * sub + (i % V);
+}
+
+// p: a staged row + V sub
+template <int R, int V>
+__device__ __forceinline__ void rec_load_rows(const float* p, float (&out)[R]) {
+#pragma unroll
+    for (int j = 0; j < R / V; ++j) {
+        if (V == 4) {
+            const float4 x = *reinterpret_cast<const float4*>(p + j * kRecLanes * V);
+            out[4 * j] = x.x; out[4 * j + 1] = x.y; out[4 * j + 2] = x.z; out[4 * j + 3] = x.w;
+        } else {
+            const float2 x = *reinterpret_cast<const float2*>(p + j * kRecLanes * V);
+            out[2 * j] = x.x; out[2 * j + 1] = x.y;
+        }
+    }
+}
+
+template <typename T, int R, bool DELTA, int B>
 __global__ void __launch_bounds__(kRecThreads)
 matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                          long long q_stride, long long k_stride, long long v_stride, int act_silu,
@@ -235,113 +267,172 @@ matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const
                          const int* __restrict__ cu_q, const int* __restrict__ state_slot,
                          float* __restrict__ y, int heads, int qk_heads, int dk, int dv) {
     constexpr int DP = R * kRecLanes;                    // padded key width
-    __shared__ float q_s[kRecBlock][DP];
-    __shared__ float k_s[kRecBlock][DP];
-    __shared__ float g_s[kRecBlock][DP];
-    __shared__ float v_s[kRecBlock][kRecCols];
-    __shared__ float b_s[kRecBlock];
+    constexpr int PL = (DP + 31) / 32;                   // key channels a staging lane holds
+    constexpr int V = R >= 4 ? 4 : R;                    // rows a state lane reads in one load
+    constexpr int kRowsPerLoader = B / kRecLoaders;
+    constexpr int kValueLoads = (B * kRecCols + kRecLoaders * 32 - 1) / (kRecLoaders * 32);
+    static_assert(B % kRecLoaders == 0, "a loader warp stages whole rows");
+    extern __shared__ __align__(16) float rec_smem[];
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x, h = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int sub = lane % kRecLanes;
-    const int col = blockIdx.z * kRecCols + warp * kRecColsPerWarp + lane / kRecLanes;
-    const int col_local = warp * kRecColsPerWarp + lane / kRecLanes;
     const int qkh = h / (heads / qk_heads);
     const bool channel_decay = a != nullptr;
-    const float rate = channel_decay ? expf(a_log[h]) : 0.f;
     const float head_decay = channel_decay ? 1.f : decay[h];
-    float* st = state + (static_cast<size_t>(state_slot[r]) * heads + h) * dk * dv;
-    float s[R];
-#pragma unroll
-    for (int i = 0; i < R; ++i) {
-        const int row = sub + kRecLanes * i;
-        s[i] = (row < dk && col < dv) ? st[static_cast<size_t>(row) * dv + col] : 0.f;
-    }
     const int first = cu_q[r], last = cu_q[r + 1];
-    for (int t0 = first; t0 < last; t0 += kRecBlock) {
-        const int n_tok = min(kRecBlock, last - t0);
-        __syncthreads();                                   // the block before has been read
-        for (int idx = tid; idx < n_tok * DP; idx += kRecThreads) {
-            const int tok = idx / DP, i = idx - tok * DP;
-            float qv = 0.f, kv = 0.f, gv = 1.f;
-            if (i < dk) {
-                const size_t t = static_cast<size_t>(t0 + tok);
-                qv = to_float(q[t * q_stride + static_cast<size_t>(qkh) * dk + i]);
-                kv = to_float(k[t * k_stride + static_cast<size_t>(qkh) * dk + i]);
-                if (act_silu) { qv = silu32(qv); kv = silu32(kv); }
-                if (channel_decay) {
-                    const size_t c = static_cast<size_t>(h) * dk + i;
-                    gv = expf(-rate * softplus32(a[t * a_stride + c] + dt_bias[c]));
-                } else {
-                    gv = head_decay;
-                }
-            }
-            q_s[tok][i] = qv;
-            k_s[tok][i] = kv;
-            g_s[tok][i] = gv;
+    const int blocks = (last - first + B - 1) / B;
+    const bool loader = warp >= kRecWarps;
+
+    // ---- loaders: stage block `blk` into buffer `blk & 1`
+    const float rate = channel_decay ? expf(a_log[h]) : 0.f;
+    float bias[PL];
+#pragma unroll
+    for (int j = 0; j < PL; ++j) {
+        const int i = lane + 32 * j;
+        bias[j] = (loader && channel_decay && i < dk) ? dt_bias[static_cast<size_t>(h) * dk + i] : 0.f;
+    }
+    auto stage = [&](int blk) {
+        float* buf = rec_smem + (blk & 1) * rec_buffer_floats(B, DP);
+        float* q_s = buf;
+        float* k_s = buf + B * DP;
+        float* g_s = buf + 2 * B * DP;
+        float* v_s = buf + 3 * B * DP;
+        float* b_s = v_s + B * kRecCols;
+        const int t0 = first + blk * B;
+        const int n_tok = min(B, last - t0);
+        const int lw = warp - kRecWarps, ltid = tid - kRecWarps * 32;
+        // every load of the block's rows is issued before the first value is used
+        float vv[kValueLoads];
+#pragma unroll
+        for (int j = 0; j < kValueLoads; ++j) {
+            const int idx = ltid + kRecLoaders * 32 * j;
+            const int tok = idx / kRecCols, cc = blockIdx.z * kRecCols + idx % kRecCols;
+            vv[j] = (tok < n_tok && cc < dv)
+                ? to_float(v[static_cast<size_t>(t0 + tok) * v_stride + static_cast<size_t>(h) * dv + cc]) : 0.f;
         }
-        for (int idx = tid; idx < n_tok * kRecCols; idx += kRecThreads) {
-            const int tok = idx / kRecCols, c = idx - tok * kRecCols;
-            const int cc = blockIdx.z * kRecCols + c;
-            float vv = 0.f;
-            if (cc < dv) {
-                vv = to_float(v[static_cast<size_t>(t0 + tok) * v_stride + static_cast<size_t>(h) * dv + cc]);
-                if (act_silu) vv = silu32(vv);
+        float bb = 0.f;
+        if (DELTA && ltid < n_tok) bb = to_float(beta[static_cast<size_t>(t0 + ltid) * beta_stride + h]);
+        float qv[kRowsPerLoader][PL], kv[kRowsPerLoader][PL], av[kRowsPerLoader][PL];
+#pragma unroll
+        for (int m = 0; m < kRowsPerLoader; ++m) {
+            const int tok = lw + kRecLoaders * m;
+            const size_t t = static_cast<size_t>(t0 + tok);
+#pragma unroll
+            for (int j = 0; j < PL; ++j) {
+                const int i = lane + 32 * j;
+                const bool in = tok < n_tok && i < dk;
+                qv[m][j] = in ? to_float(q[t * q_stride + static_cast<size_t>(qkh) * dk + i]) : 0.f;
+                kv[m][j] = in ? to_float(k[t * k_stride + static_cast<size_t>(qkh) * dk + i]) : 0.f;
+                av[m][j] = (in && channel_decay) ? a[t * a_stride + static_cast<size_t>(h) * dk + i] : 0.f;
             }
-            v_s[tok][c] = vv;
         }
-        if (DELTA && tid < n_tok) b_s[tid] = sigmoid32(to_float(beta[static_cast<size_t>(t0 + tid) * beta_stride + h]));
-        __syncthreads();
-        if (unit) {
-            // a warp per row: q and k become unit vectors; the sum over the head in lane order
-            for (int tok = warp; tok < n_tok; tok += kRecWarps) {
-                float sq = 0.f, sk = 0.f;
-                for (int i = lane; i < dk; i += 32) {
-                    sq = fmaf(q_s[tok][i], q_s[tok][i], sq);
-                    sk = fmaf(k_s[tok][i], k_s[tok][i], sk);
-                }
+#pragma unroll
+        for (int j = 0; j < kValueLoads; ++j)
+            if (ltid + kRecLoaders * 32 * j < B * kRecCols)
+                v_s[ltid + kRecLoaders * 32 * j] = act_silu ? silu32(vv[j]) : vv[j];
+        if (DELTA && ltid < n_tok) b_s[ltid] = sigmoid32(bb);
+#pragma unroll
+        for (int m = 0; m < kRowsPerLoader; ++m) {
+            const int tok = lw + kRecLoaders * m;
+            if (tok >= n_tok) break;                       // uniform in the warp
+            float sq = 0.f, sk = 0.f;
+#pragma unroll
+            for (int j = 0; j < PL; ++j) {
+                if (act_silu) { qv[m][j] = silu32(qv[m][j]); kv[m][j] = silu32(kv[m][j]); }
+                sq = fmaf(qv[m][j], qv[m][j], sq);
+                sk = fmaf(kv[m][j], kv[m][j], sk);
+            }
+            float rq = 1.f, rk = 1.f;
+            if (unit) {                                    // the sum over the head in lane order
                 sq = warp_sum(sq);
                 sk = warp_sum(sk);
-                const float rq = q_scale / sqrtf(sq + unit_eps), rk = 1.0f / sqrtf(sk + unit_eps);
-                for (int i = lane; i < dk; i += 32) {
-                    q_s[tok][i] *= rq;
-                    k_s[tok][i] *= rk;
+                rq = q_scale / sqrtf(sq + unit_eps);
+                rk = 1.0f / sqrtf(sk + unit_eps);
+            }
+#pragma unroll
+            for (int j = 0; j < PL; ++j) {
+                const int i = lane + 32 * j;
+                if (i < DP) {
+                    q_s[tok * DP + i] = unit ? qv[m][j] * rq : qv[m][j];
+                    k_s[tok * DP + i] = unit ? kv[m][j] * rk : kv[m][j];
+                    g_s[tok * DP + i] = (channel_decay && i < dk)
+                        ? expf(-rate * softplus32(av[m][j] + bias[j])) : head_decay;
                 }
             }
-            __syncthreads();
         }
-        for (int tok = 0; tok < n_tok; ++tok) {
-            float dot = 0.f;
+    };
+
+    // ---- the four state warps
+    const int sub = lane % kRecLanes;
+    const int col_local = (warp % kRecWarps) * kRecColsPerWarp + lane / kRecLanes;
+    const int col = blockIdx.z * kRecCols + col_local;
+    float* st = state + (static_cast<size_t>(state_slot[r]) * heads + h) * dk * dv;
+    float s[R];
+    if (!loader) {
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-                const int row = sub + kRecLanes * i;
-                s[i] *= g_s[tok][row];
-                if (DELTA) dot = fmaf(s[i], k_s[tok][row], dot);
-            }
-            float u = v_s[tok][col_local];
-            if (DELTA) {
-#pragma unroll
-                for (int o = kRecLanes / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                u = b_s[tok] * (u - dot);
-            }
-            float out = 0.f;
-#pragma unroll
-            for (int i = 0; i < R; ++i) {
-                const int row = sub + kRecLanes * i;
-                s[i] = fmaf(k_s[tok][row], u, s[i]);
-                out = fmaf(s[i], q_s[tok][row], out);
-            }
-#pragma unroll
-            for (int o = kRecLanes / 2; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-            if (sub == 0 && col < dv)
-                y[static_cast<size_t>(t0 + tok) * heads * dv + static_cast<size_t>(h) * dv + col] = out;
+        for (int i = 0; i < R; ++i) {
+            const int row = rec_row<V>(sub, i);
+            s[i] = (row < dk && col < dv) ? st[static_cast<size_t>(row) * dv + col] : 0.f;
         }
     }
+    auto advance = [&](int blk) {
+        const float* buf = rec_smem + (blk & 1) * rec_buffer_floats(B, DP);
+        const float* q_s = buf;
+        const float* k_s = buf + B * DP;
+        const float* g_s = buf + 2 * B * DP;
+        const float* v_s = buf + 3 * B * DP;
+        const float* b_s = v_s + B * kRecCols;
+        const int t0 = first + blk * B;
+        const int n_tok = min(B, last - t0);
+        for (int tok = 0; tok < n_tok; ++tok) {
+            float kk[R], xx[R];
+            rec_load_rows<R, V>(g_s + tok * DP + sub * V, xx);
+            rec_load_rows<R, V>(k_s + tok * DP + sub * V, kk);
+            float dot[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-        const int row = sub + kRecLanes * i;
-        if (row < dk && col < dv) st[static_cast<size_t>(row) * dv + col] = s[i];
+            for (int i = 0; i < R; ++i) {
+                s[i] *= xx[i];
+                if (DELTA) dot[i % 4] = fmaf(s[i], kk[i], dot[i % 4]);
+            }
+            float u = v_s[tok * kRecCols + col_local];
+            if (DELTA) {
+                float d = (dot[0] + dot[1]) + (dot[2] + dot[3]);
+#pragma unroll
+                for (int o = kRecLanes / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                u = b_s[tok] * (u - d);
+            }
+            rec_load_rows<R, V>(q_s + tok * DP + sub * V, xx);
+            float out[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                s[i] = fmaf(kk[i], u, s[i]);
+                out[i % 4] = fmaf(s[i], xx[i], out[i % 4]);
+            }
+            float o_sum = (out[0] + out[1]) + (out[2] + out[3]);
+#pragma unroll
+            for (int o = kRecLanes / 2; o > 0; o >>= 1) o_sum += __shfl_xor_sync(0xffffffffu, o_sum, o);
+            if (sub == 0 && col < dv)
+                y[static_cast<size_t>(t0 + tok) * heads * dv + static_cast<size_t>(h) * dv + col] = o_sum;
+        }
+    };
+
+    if (loader && blocks > 0) stage(0);
+    __syncthreads();
+    for (int blk = 0; blk < blocks; ++blk) {
+        if (loader) {
+            if (blk + 1 < blocks) stage(blk + 1);
+        } else {
+            advance(blk);
+        }
+        __syncthreads();                                   // block blk + 1 is staged, block blk is read
+    }
+    if (!loader) {
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const int row = rec_row<V>(sub, i);
+            if (row < dk && col < dv) st[static_cast<size_t>(row) * dv + col] = s[i];
+        }
     }
 }
 
@@ -389,11 +480,18 @@ __global__ void rmsnorm_pair_mean_kernel(const void* __restrict__ a, int a_dtype
     float* ra_s = pair_rows;
     float* rb_s = pair_rows + H;
     float sa = 0.f, sb = 0.f;
+    // partial sums are float32: their loads carry no branch on the type, so several are in flight
+    auto value = [](const void* p, int dtype, int splits, long long stride, size_t idx) {
+        if (dtype != SOMI_F32) return load_as_float(p, dtype, idx);
+        const float* f = static_cast<const float*>(p) + idx;
+        float x = f[0];
+#pragma unroll 8
+        for (int s = 1; s < splits; ++s) x += f[static_cast<size_t>(s) * stride];
+        return x;
+    };
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float x = load_as_float(a, a_dtype, base + i);
-        for (int s = 1; s < a_splits; ++s) x += load_as_float(a, a_dtype, static_cast<size_t>(s) * a_stride + base + i);
-        float z = load_as_float(b, b_dtype, base + i);
-        for (int s = 1; s < b_splits; ++s) z += load_as_float(b, b_dtype, static_cast<size_t>(s) * b_stride + base + i);
+        const float x = value(a, a_dtype, a_splits, a_stride, base + i);
+        const float z = value(b, b_dtype, b_splits, b_stride, base + i);
         ra_s[i] = x;
         rb_s[i] = z;
         sa = fmaf(x, x, sa);
@@ -485,7 +583,9 @@ SOMI_API int somi_matrix_state_scan_max_key() { return 32 * kRecLanes; }
 // q, k: [T, *_stride] with qk_heads heads of dk elements from the pointer on; v: heads heads of dv.
 // delta != 0: beta [T, beta_stride] logits per head, of q's dtype.  a != null: float32 [T, a_stride]
 // decay logits per head and key channel with dt_bias [heads * dk] and a_log [heads]; else
-// decay [heads].  state: float32 [slots, heads, dk, dv]; y: float32 [T, heads * dv].
+// decay [heads].  state: float32 [slots, heads, dk, dv]; y: float32 [T, heads * dv].  max_rows: the
+// most rows any request has in this step (0: not known); it only chooses how many rows are staged
+// at a time, the sums are the same.
 SOMI_API int somi_matrix_state_scan(const void* q, const void* k, const void* v, int dtype,
                                     long long q_stride, long long k_stride, long long v_stride,
                                     int act_silu, int unit, float unit_eps, float q_scale, int delta,
@@ -493,7 +593,7 @@ SOMI_API int somi_matrix_state_scan(const void* q, const void* k, const void* v,
                                     long long a_stride, const float* dt_bias, const float* a_log,
                                     const float* decay, float* state, const int* cu_q,
                                     const int* state_slot, float* y, int R, int heads, int qk_heads,
-                                    int dk, int dv, cudaStream_t stream) {
+                                    int dk, int dv, int max_rows, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (dk <= 0 || dk > 32 * kRecLanes || dv <= 0 || heads <= 0 || qk_heads <= 0 || heads % qk_heads ||
         (delta && beta == nullptr) || (a == nullptr && decay == nullptr) ||
@@ -501,19 +601,27 @@ SOMI_API int somi_matrix_state_scan(const void* q, const void* k, const void* v,
         return SOMI_ERR_UNSUPPORTED;
     dim3 grid(R, heads, (dv + kRecCols - 1) / kRecCols);
     const int rows = (dk + kRecLanes - 1) / kRecLanes;
-#define SOMI_LAUNCH_REC(TT, RR, DD)                                                               \
-    launch_pdl(matrix_state_scan_kernel<TT, RR, DD>, grid, dim3(kRecThreads), 0, stream,          \
+#define SOMI_LAUNCH_REC_B(TT, RR, DD, BB)                                                         \
+    const size_t smem = sizeof(float) * 2 * rec_buffer_floats(BB, RR * kRecLanes);                \
+    if (smem > 48 * 1024)                                                                         \
+        cudaFuncSetAttribute(matrix_state_scan_kernel<TT, RR, DD, BB>,                            \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
+    launch_pdl(matrix_state_scan_kernel<TT, RR, DD, BB>, grid, dim3(kRecThreads), smem, stream,   \
                static_cast<const TT*>(q), static_cast<const TT*>(k), static_cast<const TT*>(v),   \
                q_stride, k_stride, v_stride, act_silu, unit, unit_eps, q_scale,                 \
                static_cast<const TT*>(beta), beta_stride,                                         \
                a, a_stride, dt_bias, a_log, decay, state, cu_q, state_slot, y, heads, qk_heads, dk, dv)
+    // short steps stage little, so that more CTAs are resident while their states stream in
+#define SOMI_LAUNCH_REC(TT, RR, DD)                                                               \
+    if (max_rows > 0 && max_rows <= kRecBlockShort) { SOMI_LAUNCH_REC_B(TT, RR, DD, kRecBlockShort); } \
+    else { SOMI_LAUNCH_REC_B(TT, RR, DD, kRecBlockLong); }
 #define SOMI_REC_BY_ROWS(TT, DD)                                                                  \
     do {                                                                                          \
-        if (rows <= 2) SOMI_LAUNCH_REC(TT, 2, DD);                                                \
-        else if (rows <= 4) SOMI_LAUNCH_REC(TT, 4, DD);                                           \
-        else if (rows <= 8) SOMI_LAUNCH_REC(TT, 8, DD);                                           \
-        else if (rows <= 16) SOMI_LAUNCH_REC(TT, 16, DD);                                         \
-        else SOMI_LAUNCH_REC(TT, 32, DD);                                                         \
+        if (rows <= 2) { SOMI_LAUNCH_REC(TT, 2, DD); }                                            \
+        else if (rows <= 4) { SOMI_LAUNCH_REC(TT, 4, DD); }                                       \
+        else if (rows <= 8) { SOMI_LAUNCH_REC(TT, 8, DD); }                                       \
+        else if (rows <= 16) { SOMI_LAUNCH_REC(TT, 16, DD); }                                     \
+        else { SOMI_LAUNCH_REC(TT, 32, DD); }                                                     \
     } while (0)
     if (dtype == SOMI_F32) {
         if (delta) SOMI_REC_BY_ROWS(float, true);
@@ -524,6 +632,7 @@ SOMI_API int somi_matrix_state_scan(const void* q, const void* k, const void* v,
     }
 #undef SOMI_REC_BY_ROWS
 #undef SOMI_LAUNCH_REC
+#undef SOMI_LAUNCH_REC_B
     return launch_status();
 }
 
@@ -555,7 +664,8 @@ SOMI_API int somi_rmsnorm_pair_mean(const void* a, int a_dtype, int a_splits, lo
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(rmsnorm_pair_mean_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem);
-    launch_pdl(rmsnorm_pair_mean_kernel, dim3(T), dim3(threads_for(H)), smem, stream, a, a_dtype,
+    const int threads = min(1024, max(32, ((H / 4 + 31) / 32) * 32));
+    launch_pdl(rmsnorm_pair_mean_kernel, dim3(T), dim3(threads), smem, stream, a, a_dtype,
                a_splits, a_stride, b, b_dtype, b_splits, b_stride, wa, wb, w_dtype, eps, out, H);
     return launch_status();
 }

@@ -1135,7 +1135,8 @@ class CudaOps:
             ctypes.c_longlong(decay_logits.stride(0) if decay_logits is not None else 0),
             _ptr(dt_bias), _ptr(a_log), _ptr(decay), _ptr(state), _ptr(batch.cu_q),
             _ptr(batch.state_slot), _ptr(y), ctypes.c_int(batch.num_requests), ctypes.c_int(heads),
-            ctypes.c_int(qk_heads), ctypes.c_int(dk), ctypes.c_int(dv), self._stream())
+            ctypes.c_int(qk_heads), ctypes.c_int(dk), ctypes.c_int(dv),
+            ctypes.c_int(int(getattr(batch, "max_q_len", 0) or 0)), self._stream())
         self._done(rc, "matrix_state_scan")
         if trace.active():
             T = q.shape[0]

@@ -363,6 +363,36 @@ def test_decayed_sum_over_steps(ops, dtype, geometry):
         assert (got[r] - ref).abs().max().item() < 2e-5 * max(1.0, ref.abs().max().item()), r
 
 
+@pytest.mark.parametrize("delta", [False, True])
+def test_scan_staging_does_not_change_the_sums(ops, delta):
+    """A step in which no request has more than four rows stages fewer rows at a time; y and the
+    state are bit for bit those of the long staging."""
+    import dataclasses
+    H, d, dv = 3, 24, 20
+    g = torch.Generator().manual_seed(5)
+    outs = []
+    for known in (True, False):
+        steps = Steps(ops, 3, state=StateNeeds({"m": ((H, d, dv), torch.float32)}), dtype=torch.float32)
+        state = steps.mgr.view(0).state["m"]
+        g.manual_seed(5)
+        ys = []
+        for counts in ({"a": 4, "b": 1, "c": 3}, {"a": 2, "b": 4}, {"c": 1, "a": 1}):
+            batch, _ = steps.step(counts)
+            assert batch.max_q_len <= 4
+            if not known:
+                batch = dataclasses.replace(batch, max_q_len=0)
+            n = batch.num_tokens
+            q, k = torch.randn((n, H * d), generator=g).cuda(), torch.randn((n, H * d), generator=g).cuda()
+            v, beta = torch.randn((n, H * dv), generator=g).cuda(), torch.randn((n, H), generator=g).cuda()
+            y = torch.empty((n, H * dv), dtype=torch.float32, device="cuda")
+            ops.matrix_state_scan(q, k, v, state, batch, y, H, H, d, dv, unit_eps=1e-6,
+                                  beta=beta if delta else None, decay=torch.tensor([0.9, 1.0, 0.5]).cuda())
+            ys.append(y.cpu())
+        outs.append((torch.cat(ys), state.cpu().clone()))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert outs[0][0].abs().max().item() > 0.1
+
+
 def test_a_state_keeps_a_token_written_long_before(ops):
     """A key along one axis, written once, is read back 400 single-token steps later through a
     state that forgets nothing on that axis (decay 1), while every other token writes along other
