@@ -204,15 +204,17 @@ __global__ void headnorm_rotary_store_kernel(T* __restrict__ qkv, long long stri
 }
 
 // ------------------------------------------------------- matrix-state recurrence
-// Per request r and head h a state S [dk, dv] float32 in the request's slot; per token, in order:
+// Per request r and head h a state S [dk, dv] float32 in the request's slot (stored column by
+// column, [dv][dk]); per token, in order:
 //     S <- g .* S         g: decay[h] (a constant), or per key channel i
 //                         g_i = exp(-exp(a_log[h]) * softplus(a[t, h dk + i] + dt_bias[h dk + i]))
 //     u = v                                   (DELTA false)
 //     u = sigmoid(b[t, h]) * (v - S^T k)      (DELTA true)
 //     S <- S + k u^T;   y[t, h, :] = S^T q.
-// q and k of head h are head h / (heads / qk_heads) of their tensors.  With `act_silu` q, k and v
-// pass SiLU as they are read; with `unit` q and k are divided by sqrt(sum of squares + unit_eps)
-// and q is multiplied by q_scale.
+// q and k of head h are head h / (heads / qk_heads) of their tensors.  With `act_silu` q and k
+// (bit 0) and v (bit 1) pass SiLU as they are read; with `unit` q and k are divided by
+// sqrt(sum of squares + unit_eps) and q is multiplied by q_scale.  v and beta are read by their
+// own dtype code; with `decay_ready` a holds the decays g themselves.
 // A CTA owns kRecCols columns of S for one (request, head) and walks through the request's rows
 // of this step, kRecBlock rows at a time.  Four warps hold the state: a column is held by 8 lanes,
 // each lane runs of four neighbouring rows; the sums over rows are taken in a fixed order (four
@@ -236,11 +238,6 @@ __host__ __device__ constexpr int rec_buffer_floats(int B, int DP) {
 
 // A state lane `sub` of 8 holds R rows in runs of V neighbours: entry i is row
 // 8 V (i / V) + V sub + i % V, so that the 8 lanes read 8 V neighbouring floats with one load each.
-template <int V>
-__device__ __forceinline__ int rec_row(int sub, int i) {
-    return kRecLanes * V * (i / V) + V * sub + (i % V);
-}
-
 // p: a staged row + V sub
 template <int R, int V>
 __device__ __forceinline__ void rec_load_rows(const float* p, float (&out)[R]) {
@@ -256,12 +253,52 @@ __device__ __forceinline__ void rec_load_rows(const float* p, float (&out)[R]) {
     }
 }
 
+// The rows of one column of a state (col: the column's dk floats) that lane `sub` holds, read
+// into or written from s.  `runs`: dk is a multiple of V and the column starts on a 16-byte
+// boundary, so a run of V rows is one access.
+template <int R, int V, bool STORE>
+__device__ __forceinline__ void rec_state_rows(float* col, float (&s)[R], int sub, int dk, bool live,
+                                               bool runs) {
+#pragma unroll
+    for (int j = 0; j < R / V; ++j) {
+        const int row = kRecLanes * V * j + V * sub;
+        if (runs) {
+            const bool in = live && row < dk;
+            if (V == 4) {
+                float4* p = reinterpret_cast<float4*>(col + row);
+                if (STORE) {
+                    if (in) *p = make_float4(s[4 * j], s[4 * j + 1], s[4 * j + 2], s[4 * j + 3]);
+                } else {
+                    const float4 x = in ? *p : make_float4(0.f, 0.f, 0.f, 0.f);
+                    s[4 * j] = x.x; s[4 * j + 1] = x.y; s[4 * j + 2] = x.z; s[4 * j + 3] = x.w;
+                }
+            } else {
+                float2* p = reinterpret_cast<float2*>(col + row);
+                if (STORE) {
+                    if (in) *p = make_float2(s[2 * j], s[2 * j + 1]);
+                } else {
+                    const float2 x = in ? *p : make_float2(0.f, 0.f);
+                    s[2 * j] = x.x; s[2 * j + 1] = x.y;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const bool in = live && row + e < dk;
+                if (STORE) { if (in) col[row + e] = s[V * j + e]; }
+                else s[V * j + e] = in ? col[row + e] : 0.f;
+            }
+        }
+    }
+}
+
 template <typename T, int R, bool DELTA, int B>
-__global__ void __launch_bounds__(kRecThreads)
-matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
-                         long long q_stride, long long k_stride, long long v_stride, int act_silu,
-                         int unit, float unit_eps, float q_scale, const T* __restrict__ beta,
-                         long long beta_stride, const float* __restrict__ a, long long a_stride,
+__global__ void __launch_bounds__(kRecThreads, (B == kRecBlockShort && R <= 16) ? 4 : 1)
+matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const void* __restrict__ v,
+                         int vb_dtype, long long q_stride, long long k_stride, long long v_stride,
+                         int act_silu, int unit, float unit_eps, float q_scale,
+                         const void* __restrict__ beta, long long beta_stride,
+                         const float* __restrict__ a, long long a_stride, int decay_ready,
                          const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                          const float* __restrict__ decay, float* __restrict__ state,
                          const int* __restrict__ cu_q, const int* __restrict__ state_slot,
@@ -309,10 +346,11 @@ matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const
             const int idx = ltid + kRecLoaders * 32 * j;
             const int tok = idx / kRecCols, cc = blockIdx.z * kRecCols + idx % kRecCols;
             vv[j] = (tok < n_tok && cc < dv)
-                ? to_float(v[static_cast<size_t>(t0 + tok) * v_stride + static_cast<size_t>(h) * dv + cc]) : 0.f;
+                ? load_as_float(v, vb_dtype, static_cast<size_t>(t0 + tok) * v_stride + static_cast<size_t>(h) * dv + cc) : 0.f;
         }
         float bb = 0.f;
-        if (DELTA && ltid < n_tok) bb = to_float(beta[static_cast<size_t>(t0 + ltid) * beta_stride + h]);
+        if (DELTA && ltid < n_tok)
+            bb = load_as_float(beta, vb_dtype, static_cast<size_t>(t0 + ltid) * beta_stride + h);
         float qv[kRowsPerLoader][PL], kv[kRowsPerLoader][PL], av[kRowsPerLoader][PL];
 #pragma unroll
         for (int m = 0; m < kRowsPerLoader; ++m) {
@@ -330,7 +368,7 @@ matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const
 #pragma unroll
         for (int j = 0; j < kValueLoads; ++j)
             if (ltid + kRecLoaders * 32 * j < B * kRecCols)
-                v_s[ltid + kRecLoaders * 32 * j] = act_silu ? silu32(vv[j]) : vv[j];
+                v_s[ltid + kRecLoaders * 32 * j] = (act_silu & 2) ? silu32(vv[j]) : vv[j];
         if (DELTA && ltid < n_tok) b_s[ltid] = sigmoid32(bb);
 #pragma unroll
         for (int m = 0; m < kRowsPerLoader; ++m) {
@@ -339,7 +377,7 @@ matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const
             float sq = 0.f, sk = 0.f;
 #pragma unroll
             for (int j = 0; j < PL; ++j) {
-                if (act_silu) { qv[m][j] = silu32(qv[m][j]); kv[m][j] = silu32(kv[m][j]); }
+                if (act_silu & 1) { qv[m][j] = silu32(qv[m][j]); kv[m][j] = silu32(kv[m][j]); }
                 sq = fmaf(qv[m][j], qv[m][j], sq);
                 sk = fmaf(kv[m][j], kv[m][j], sk);
             }
@@ -357,7 +395,8 @@ matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const
                     q_s[tok * DP + i] = unit ? qv[m][j] * rq : qv[m][j];
                     k_s[tok * DP + i] = unit ? kv[m][j] * rk : kv[m][j];
                     g_s[tok * DP + i] = (channel_decay && i < dk)
-                        ? expf(-rate * softplus32(av[m][j] + bias[j])) : head_decay;
+                        ? (decay_ready ? av[m][j] : expf(-rate * softplus32(av[m][j] + bias[j])))
+                        : head_decay;
                 }
             }
         }
@@ -367,15 +406,13 @@ matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const
     const int sub = lane % kRecLanes;
     const int col_local = (warp % kRecWarps) * kRecColsPerWarp + lane / kRecLanes;
     const int col = blockIdx.z * kRecCols + col_local;
-    float* st = state + (static_cast<size_t>(state_slot[r]) * heads + h) * dk * dv;
+    // a head's matrix is stored column by column ([dv][dk]): the 8 lanes of a column read
+    // neighbouring runs of one line
+    float* st = state + (static_cast<size_t>(state_slot[r]) * heads + h) * dk * dv
+        + static_cast<size_t>(col) * dk;
+    const bool runs = dk % V == 0 && (reinterpret_cast<uintptr_t>(state) & 15) == 0;
     float s[R];
-    if (!loader) {
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-            const int row = rec_row<V>(sub, i);
-            s[i] = (row < dk && col < dv) ? st[static_cast<size_t>(row) * dv + col] : 0.f;
-        }
-    }
+    if (!loader) rec_state_rows<R, V, false>(st, s, sub, dk, col < dv, runs);
     auto advance = [&](int blk) {
         const float* buf = rec_smem + (blk & 1) * rec_buffer_floats(B, DP);
         const float* q_s = buf;
@@ -427,11 +464,76 @@ matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const
         }
         __syncthreads();                                   // block blk + 1 is staged, block blk is read
     }
-    if (!loader) {
+    if (!loader) rec_state_rows<R, V, true>(st, s, sub, dk, col < dv, runs);
+}
+
+// ------------------------------------------- rows of a long step, made ready once
+// The CTAs of a head's column groups all need the same q, k and g of a row.  For a step of many
+// rows this kernel computes them once, with the arithmetic of the scan's loaders in the same
+// order (so the scan's result is the same bit for bit), and the scan's loaders only copy:
+//     qn[t, qk head, :], kn[t, qk head, :]  activated and unit-normed, float32
+//     gd[t, head, :] = exp(-exp(a_log) * softplus(a + dt_bias))          (a != null)
+// A warp per (row, head); q and k are written by the first head of each query/key head's group.
+constexpr int kRecPrepWarps = 4;
+constexpr int kRecMaxPL = 8;                              // key widths up to 32 * kRecLanes
+
+template <typename T>
+__global__ void __launch_bounds__(kRecPrepWarps * 32)
+matrix_state_prepare_kernel(const T* __restrict__ q, const T* __restrict__ k, long long q_stride,
+                            long long k_stride, int act_silu, int unit, float unit_eps, float q_scale,
+                            const float* __restrict__ a, long long a_stride,
+                            const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                            float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ gd,
+                            int rows, int heads, int qk_heads, int dk) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * kRecPrepWarps + (threadIdx.x >> 5);
+    const int h = blockIdx.y;
+    if (t >= rows) return;
+    const int group = heads / qk_heads, qkh = h / group;
+    const size_t row = static_cast<size_t>(t);
+    if (a != nullptr) {
+        const float rate = expf(a_log[h]);
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-            const int row = rec_row<V>(sub, i);
-            if (row < dk && col < dv) st[static_cast<size_t>(row) * dv + col] = s[i];
+        for (int j = 0; j < kRecMaxPL; ++j) {
+            const int i = lane + 32 * j;
+            if (i < dk) {
+                const size_t c = static_cast<size_t>(h) * dk + i;
+                gd[row * heads * dk + c] = expf(-rate * softplus32(a[row * a_stride + c] + dt_bias[c]));
+            }
+        }
+    }
+    if (h % group) return;
+    float qv[kRecMaxPL], kv[kRecMaxPL];
+    float sq = 0.f, sk = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRecMaxPL; ++j) {
+        const int i = lane + 32 * j;
+        const bool in = i < dk;
+        qv[j] = in ? to_float(q[row * q_stride + static_cast<size_t>(qkh) * dk + i]) : 0.f;
+        kv[j] = in ? to_float(k[row * k_stride + static_cast<size_t>(qkh) * dk + i]) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kRecMaxPL; ++j) {
+        if (act_silu & 1) { qv[j] = silu32(qv[j]); kv[j] = silu32(kv[j]); }
+        sq = fmaf(qv[j], qv[j], sq);
+        sk = fmaf(kv[j], kv[j], sk);
+    }
+    float rq = 1.f, rk = 1.f;
+    if (unit) {
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        rq = q_scale / sqrtf(sq + unit_eps);
+        rk = 1.0f / sqrtf(sk + unit_eps);
+    }
+#pragma unroll
+    for (int j = 0; j < kRecMaxPL; ++j) {
+        const int i = lane + 32 * j;
+        if (i < dk) {
+            const size_t c = row * qk_heads * dk + static_cast<size_t>(qkh) * dk + i;
+            qn[c] = unit ? qv[j] * rq : qv[j];
+            kn[c] = unit ? kv[j] * rk : kv[j];
         }
     }
 }
@@ -583,14 +685,16 @@ SOMI_API int somi_matrix_state_scan_max_key() { return 32 * kRecLanes; }
 // q, k: [T, *_stride] with qk_heads heads of dk elements from the pointer on; v: heads heads of dv.
 // delta != 0: beta [T, beta_stride] logits per head, of q's dtype.  a != null: float32 [T, a_stride]
 // decay logits per head and key channel with dt_bias [heads * dk] and a_log [heads]; else
-// decay [heads].  state: float32 [slots, heads, dk, dv]; y: float32 [T, heads * dv].  max_rows: the
+// decay [heads] (decay_ready: a holds the decays).  dtype: of q and k; vb_dtype: of v and beta.
+// state: float32 [slots, heads, dv, dk]; y: float32 [T, heads * dv].  max_rows: the
 // most rows any request has in this step (0: not known); it only chooses how many rows are staged
 // at a time, the sums are the same.
 SOMI_API int somi_matrix_state_scan(const void* q, const void* k, const void* v, int dtype,
-                                    long long q_stride, long long k_stride, long long v_stride,
-                                    int act_silu, int unit, float unit_eps, float q_scale, int delta,
-                                    const void* beta, long long beta_stride, const float* a,
-                                    long long a_stride, const float* dt_bias, const float* a_log,
+                                    int vb_dtype, long long q_stride, long long k_stride,
+                                    long long v_stride, int act_silu, int unit, float unit_eps,
+                                    float q_scale, int delta, const void* beta, long long beta_stride,
+                                    const float* a, long long a_stride, int decay_ready,
+                                    const float* dt_bias, const float* a_log,
                                     const float* decay, float* state, const int* cu_q,
                                     const int* state_slot, float* y, int R, int heads, int qk_heads,
                                     int dk, int dv, int max_rows, cudaStream_t stream) {
@@ -607,10 +711,9 @@ SOMI_API int somi_matrix_state_scan(const void* q, const void* k, const void* v,
         cudaFuncSetAttribute(matrix_state_scan_kernel<TT, RR, DD, BB>,                            \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
     launch_pdl(matrix_state_scan_kernel<TT, RR, DD, BB>, grid, dim3(kRecThreads), smem, stream,   \
-               static_cast<const TT*>(q), static_cast<const TT*>(k), static_cast<const TT*>(v),   \
+               static_cast<const TT*>(q), static_cast<const TT*>(k), v, vb_dtype,                 \
                q_stride, k_stride, v_stride, act_silu, unit, unit_eps, q_scale,                 \
-               static_cast<const TT*>(beta), beta_stride,                                         \
-               a, a_stride, dt_bias, a_log, decay, state, cu_q, state_slot, y, heads, qk_heads, dk, dv)
+               beta, beta_stride, a, a_stride, decay_ready, dt_bias, a_log, decay, state, cu_q, state_slot, y, heads, qk_heads, dk, dv)
     // short steps stage little, so that more CTAs are resident while their states stream in
 #define SOMI_LAUNCH_REC(TT, RR, DD)                                                               \
     if (max_rows > 0 && max_rows <= kRecBlockShort) { SOMI_LAUNCH_REC_B(TT, RR, DD, kRecBlockShort); } \
@@ -633,6 +736,32 @@ SOMI_API int somi_matrix_state_scan(const void* q, const void* k, const void* v,
 #undef SOMI_REC_BY_ROWS
 #undef SOMI_LAUNCH_REC
 #undef SOMI_LAUNCH_REC_B
+    return launch_status();
+}
+
+// q, k: [T, *_stride] of `dtype` -> qn, kn: float32 [T, qk_heads * dk]; a (may be null) ->
+// gd: float32 [T, heads * dk].  See matrix_state_prepare_kernel.
+SOMI_API int somi_matrix_state_prepare(const void* q, const void* k, int dtype, long long q_stride,
+                                       long long k_stride, int act_silu, int unit, float unit_eps,
+                                       float q_scale, const float* a, long long a_stride,
+                                       const float* dt_bias, const float* a_log, float* qn, float* kn,
+                                       float* gd, int T, int heads, int qk_heads, int dk,
+                                       cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (dk <= 0 || dk > 32 * kRecMaxPL || heads <= 0 || qk_heads <= 0 || heads % qk_heads ||
+        (a != nullptr && (dt_bias == nullptr || a_log == nullptr || gd == nullptr)))
+        return SOMI_ERR_UNSUPPORTED;
+    const dim3 grid((T + kRecPrepWarps - 1) / kRecPrepWarps, heads);
+    if (dtype == SOMI_F32)
+        launch_pdl(matrix_state_prepare_kernel<float>, grid, dim3(kRecPrepWarps * 32), 0, stream,
+                   static_cast<const float*>(q), static_cast<const float*>(k), q_stride, k_stride,
+                   act_silu, unit, unit_eps, q_scale, a, a_stride, dt_bias, a_log, qn, kn, gd, T, heads,
+                   qk_heads, dk);
+    else
+        launch_pdl(matrix_state_prepare_kernel<__nv_bfloat16>, grid, dim3(kRecPrepWarps * 32), 0, stream,
+                   static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), q_stride,
+                   k_stride, act_silu, unit, unit_eps, q_scale, a, a_stride, dt_bias, a_log, qn, kn, gd,
+                   T, heads, qk_heads, dk);
     return launch_status();
 }
 

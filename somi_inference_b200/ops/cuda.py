@@ -1104,39 +1104,68 @@ class CudaOps:
             raise KernelError(f"a matrix-state mixer with {heads} heads over {qk_heads} query/key "
                               f"heads of width {dk} is not supported (key width up to {most})")
 
+    # a step in which some request has more rows than this has q, k and the decays made ready
+    # once per row by a kernel of their own instead of once per group of state columns
+    SCAN_PREPARE_ROWS = 16
+
     def matrix_state_scan(self, q, k, v, state, batch, y, heads, qk_heads, dk, dv, *,
                           act_silu=False, unit_eps=None, q_scale=1.0, beta=None, decay_logits=None,
-                          dt_bias=None, a_log=None, decay=None) -> None:
-        """Per request and head a float32 state S [dk, dv] in `state` [slots, heads, dk, dv],
-        continued over the request's rows of this step:
+                          dt_bias=None, a_log=None, decay=None, prepare=None) -> None:
+        """Per request and head a float32 state S [dk, dv] in `state` [slots, heads, dv, dk] (a
+        head's matrix column by column), continued over the request's rows of this step:
             S <- g * S;  u = v, or with `beta` u = sigmoid(beta) * (v - S^T k);  S <- S + k u^T;
             y = S^T q
         g is `decay` [heads], or per key channel exp(-exp(a_log) * softplus(decay_logits +
         dt_bias)) (`decay_logits` float32 [T, heads * dk], rows may lie further apart).  q, k
         ([T, qk_heads * dk]) and v ([T, heads * dv]) may be views of wider rows; `act_silu`: they
         pass SiLU as they are read; `unit_eps`: q and k are divided by sqrt(sum of squares + it)
-        and q is multiplied by `q_scale`.  y: float32 [T, heads * dv]."""
+        and q is multiplied by `q_scale`.  y: float32 [T, heads * dv].  `prepare` (None: by the
+        step's longest request) only chooses where q, k and g are computed; y is the same."""
         _check(state, y, dt_bias, a_log, decay)
         for t in (q, k, v, beta, decay_logits):
             if t is not None and not (t.is_cuda and t.stride(1) == 1):
                 raise KernelError("matrix_state_scan takes device tensors with contiguous rows")
         assert q.dtype == k.dtype == v.dtype and (beta is None or beta.dtype == q.dtype)
-        assert state.dtype == y.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dk, dv)
+        assert state.dtype == y.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dv, dk)
         assert decay_logits is None or decay_logits.dtype == torch.float32
         for t in (dt_bias, a_log, decay):
             assert t is None or t.dtype == torch.float32
+        max_rows = int(getattr(batch, "max_q_len", 0) or 0)
+        if prepare is None:
+            prepare = max_rows > self.SCAN_PREPARE_ROWS
+        act, unit, ready = (3 if act_silu else 0), (0 if unit_eps is None else 1), 0
+        vb_code = _code(v)
+        if prepare:
+            T, n = q.shape[0], q.shape[0] * qk_heads * dk
+            n_g = T * heads * dk if decay_logits is not None else 0
+            buf = torch.empty(2 * n + n_g, dtype=torch.float32, device=q.device)
+            qn, kn = buf[:n].view(T, -1), buf[n:2 * n].view(T, -1)
+            gd = buf[2 * n:].view(T, -1) if n_g else None
+            rc = self.lib.somi_matrix_state_prepare(
+                _ptr(q), _ptr(k), _code(q), ctypes.c_longlong(q.stride(0)), ctypes.c_longlong(k.stride(0)),
+                ctypes.c_int(act), ctypes.c_int(unit), ctypes.c_float(unit_eps or 0.0),
+                ctypes.c_float(q_scale), _ptr(decay_logits),
+                ctypes.c_longlong(decay_logits.stride(0) if decay_logits is not None else 0),
+                _ptr(dt_bias), _ptr(a_log), _ptr(qn), _ptr(kn), _ptr(gd), ctypes.c_int(T),
+                ctypes.c_int(heads), ctypes.c_int(qk_heads), ctypes.c_int(dk), self._stream())
+            self._done(rc, "matrix_state_prepare")
+            if trace.active():
+                trace.note("matrix_state_prepare", 2 * n * (q.element_size() + 4) + 2 * n_g * 4)
+            q, k, decay_logits = qn, kn, gd
+            act, unit, ready = act & 2, 0, 1
         rc = self.lib.somi_matrix_state_scan(
-            _ptr(q), _ptr(k), _ptr(v), _code(q), ctypes.c_longlong(q.stride(0)),
+            _ptr(q), _ptr(k), _ptr(v), _code(q), vb_code, ctypes.c_longlong(q.stride(0)),
             ctypes.c_longlong(k.stride(0)), ctypes.c_longlong(v.stride(0)),
-            ctypes.c_int(1 if act_silu else 0), ctypes.c_int(0 if unit_eps is None else 1),
+            ctypes.c_int(act), ctypes.c_int(unit),
             ctypes.c_float(unit_eps or 0.0), ctypes.c_float(q_scale),
             ctypes.c_int(0 if beta is None else 1), _ptr(beta),
             ctypes.c_longlong(beta.stride(0) if beta is not None else 0), _ptr(decay_logits),
             ctypes.c_longlong(decay_logits.stride(0) if decay_logits is not None else 0),
+            ctypes.c_int(ready),
             _ptr(dt_bias), _ptr(a_log), _ptr(decay), _ptr(state), _ptr(batch.cu_q),
             _ptr(batch.state_slot), _ptr(y), ctypes.c_int(batch.num_requests), ctypes.c_int(heads),
             ctypes.c_int(qk_heads), ctypes.c_int(dk), ctypes.c_int(dv),
-            ctypes.c_int(int(getattr(batch, "max_q_len", 0) or 0)), self._stream())
+            ctypes.c_int(max_rows), self._stream())
         self._done(rc, "matrix_state_scan")
         if trace.active():
             T = q.shape[0]

@@ -1,7 +1,7 @@
 """Mixers that carry a matrix per head from token to token instead of a cache of keys.
 
-Both keep, per request and head, a float32 state M [key width, value width] that starts at zero,
-lives in the request's state slot and is read out by the token's query:
+Both keep, per request and head, a float32 state M [key width, value width] (stored column by
+column) that starts at zero, lives in the request's state slot and is read out by the token's query:
 
 `delta_rule` (the gated delta rule with a decay per key channel).  With h the mixer's input,
 H heads over G query/key heads (head i reads query/key head i // (H / G)):
@@ -101,7 +101,7 @@ class DeltaRuleMixer:
         self.out = Linear(tensors[n["o_weight"]], None, ctx.ops)
 
     def cache_needs(self) -> CacheNeeds:
-        state = {self.STATE: ((self.heads, self.key_dim, self.value_dim), torch.float32)}
+        state = {self.STATE: ((self.heads, self.value_dim, self.key_dim), torch.float32)}
         if self.taps > 1:
             state[self.STATE_CONV] = ((self.taps - 1, self.conv_width), self.ctx.dtype)
         return CacheNeeds(paged=None, state=StateNeeds(state))
@@ -164,7 +164,7 @@ class DecaySumMixer:
 
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds(paged=None, state=StateNeeds(
-            {self.STATE: ((self.heads, self.key_dim, self.value_dim), torch.float32)}))
+            {self.STATE: ((self.heads, self.value_dim, self.key_dim), torch.float32)}))
 
     def forward(self, x: torch.Tensor, batch, cache, owns_cache: bool) -> torch.Tensor:
         ops = self.ctx.ops

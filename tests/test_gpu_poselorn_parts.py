@@ -299,7 +299,7 @@ def test_delta_rule_over_steps(ops, dtype, geometry):
     over fewer query/key heads, inputs that are views of wider rows."""
     H, G, d, dv = geometry
     g = torch.Generator().manual_seed(d)
-    steps = Steps(ops, 3, state=StateNeeds({"m": ((H, d, dv), torch.float32)}), dtype=dtype)
+    steps = Steps(ops, 3, state=StateNeeds({"m": ((H, dv, d), torch.float32)}), dtype=dtype)
     L = 60
     seqs = {r: {"qkv": torch.randn((L, 2 * G * d + H * dv + 3), generator=g).to(dtype),
                 "beta": torch.randn((L, H + 2), generator=g).to(dtype),
@@ -338,7 +338,7 @@ def test_delta_rule_over_steps(ops, dtype, geometry):
 def test_decayed_sum_over_steps(ops, dtype, geometry):
     H, d, dv = geometry
     g = torch.Generator().manual_seed(d)
-    steps = Steps(ops, 3, state=StateNeeds({"m": ((H, d, dv), torch.float32)}), dtype=dtype)
+    steps = Steps(ops, 3, state=StateNeeds({"m": ((H, dv, d), torch.float32)}), dtype=dtype)
     L = 60
     seqs = {r: {"qkv": torch.randn((L, 2 * H * d + 2 * H * dv), generator=g).to(dtype)} for r in "abc"}
     decay = torch.tensor([0.3, 0.9, 1.0, 0.999, 0.6][:H])
@@ -372,7 +372,7 @@ def test_scan_staging_does_not_change_the_sums(ops, delta):
     g = torch.Generator().manual_seed(5)
     outs = []
     for known in (True, False):
-        steps = Steps(ops, 3, state=StateNeeds({"m": ((H, d, dv), torch.float32)}), dtype=torch.float32)
+        steps = Steps(ops, 3, state=StateNeeds({"m": ((H, dv, d), torch.float32)}), dtype=torch.float32)
         state = steps.mgr.view(0).state["m"]
         g.manual_seed(5)
         ys = []
@@ -393,12 +393,46 @@ def test_scan_staging_does_not_change_the_sums(ops, delta):
     assert outs[0][0].abs().max().item() > 0.1
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("delta", [False, True])
+def test_rows_made_ready_ahead_do_not_change_the_sums(ops, dtype, delta):
+    """A long step has q, k and the decays of its rows computed once by a kernel of their own;
+    y and the state are bit for bit those of the scan that computes them as it goes."""
+    H, G, d, dv = (6, 3, 40, 24) if delta else (3, 3, 24, 20)
+    outs = []
+    for prepare in (True, False):
+        steps = Steps(ops, 3, state=StateNeeds({"m": ((H, dv, d), torch.float32)}), dtype=dtype)
+        state = steps.mgr.view(0).state["m"]
+        g = torch.Generator().manual_seed(11)
+        dt_bias, a_log = 0.5 * torch.randn(H * d, generator=g), 0.7 * torch.randn(H, generator=g)
+        ys = []
+        for counts in ({"a": 37, "b": 5, "c": 20}, {"a": 2, "b": 33}):
+            batch, _ = steps.step(counts)
+            n = batch.num_tokens
+            x = torch.randn((n, 2 * G * d + H * dv + 1), generator=g).to(dtype).cuda()
+            beta = torch.randn((n, H), generator=g).to(dtype).cuda()
+            a = torch.randn((n, H * d), generator=g).cuda()
+            y = torch.empty((n, H * dv), dtype=torch.float32, device="cuda")
+            q, k, v = x[:, :G * d], x[:, G * d:2 * G * d], x[:, 2 * G * d:-1]
+            if delta:
+                ops.matrix_state_scan(q, k, v, state, batch, y, H, G, d, dv, unit_eps=1e-6, q_scale=0.3,
+                                      beta=beta, decay_logits=a, dt_bias=dt_bias.cuda(), a_log=a_log.cuda(),
+                                      prepare=prepare)
+            else:
+                ops.matrix_state_scan(q, k, v, state, batch, y, H, G, d, dv, act_silu=True,
+                                      decay=torch.tensor([0.9, 1.0, 0.5]).cuda(), prepare=prepare)
+            ys.append(y.cpu())
+        outs.append((torch.cat(ys), state.cpu().clone()))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert outs[0][0].abs().max().item() > 0.1
+
+
 def test_a_state_keeps_a_token_written_long_before(ops):
     """A key along one axis, written once, is read back 400 single-token steps later through a
     state that forgets nothing on that axis (decay 1), while every other token writes along other
     axes; with a decay below one on the second head the same token has faded to decay^400."""
     H, d, dv = 2, 8, 4
-    steps = Steps(ops, 2, state=StateNeeds({"m": ((H, d, dv), torch.float32)}), dtype=torch.float32,
+    steps = Steps(ops, 2, state=StateNeeds({"m": ((H, dv, d), torch.float32)}), dtype=torch.float32,
                   max_len=512)
     state = steps.mgr.view(0).state["m"]
     decay = torch.tensor([1.0, 0.99])
