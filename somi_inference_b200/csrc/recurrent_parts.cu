@@ -216,16 +216,17 @@ __global__ void headnorm_rotary_store_kernel(T* __restrict__ qkv, long long stri
 // sqrt(sum of squares + unit_eps) and q is multiplied by q_scale.  v and beta are read by their
 // own dtype code; with `decay_ready` a holds the decays g themselves.
 // A CTA owns kRecCols columns of S for one (request, head) and walks through the request's rows
-// of this step, kRecBlock rows at a time.  Four warps hold the state: a column is held by 8 lanes,
-// each lane runs of four neighbouring rows; the sums over rows are taken in a fixed order (four
-// partial sums per lane, each ascending, added in pairs, then a butterfly over the 8 lanes), so y
-// does not depend on how the rows were cut into steps.  Four more warps stage the next block meanwhile: they read q, k,
-// the decay logits, v and beta of its rows, apply the activations, the unit norms and the decay's
-// exponentials (a warp per row) and leave float32 values in the other of two shared buffers.
-constexpr int kRecLanes = 8;
+// of this step, B rows at a time (16, or 4 when no request has more rows than that).  Four warps
+// hold the state, four columns each, every lane a few rows of all four (RecShape below); the sums
+// over rows are taken in a fixed order (ascending in a lane, then the exchanges of rec_reduce4),
+// so y does not depend on how the rows were cut into steps.  Four more warps stage the next block
+// meanwhile: they read q, k, the decay logits, v and beta of its rows, apply the activations, the
+// unit norms and the decay's exponentials (a warp per row) and leave float32 values in the other
+// of two shared buffers.
+constexpr int kRecLanes = 8;                             // key widths are padded to 8 R, R a power of two
 constexpr int kRecWarps = 4;
 constexpr int kRecLoaders = 4;
-constexpr int kRecColsPerWarp = 32 / kRecLanes;
+constexpr int kRecColsPerWarp = 4;
 constexpr int kRecCols = kRecWarps * kRecColsPerWarp;
 constexpr int kRecBlockLong = 16;                        // rows staged at a time in a long step
 constexpr int kRecBlockShort = 4;                        // and in a step of few rows per request
@@ -236,33 +237,49 @@ __host__ __device__ constexpr int rec_buffer_floats(int B, int DP) {
     return B * (3 * DP + kRecCols + 1);
 }
 
-// A state lane `sub` of 8 holds R rows in runs of V neighbours: entry i is row
-// 8 V (i / V) + V sub + i % V, so that the 8 lanes read 8 V neighbouring floats with one load each.
-// p: a staged row + V sub
-template <int R, int V>
-__device__ __forceinline__ void rec_load_rows(const float* p, float (&out)[R]) {
+// A state warp holds kRecColsPerWarp columns.  With DP = 8 R the padded key width, a lane holds
+// RL = V J rows of each of them: J runs of V neighbours, entry (j, e) being row 32 V j + V lane + e
+// (V = 4 from a width of 128 on, else DP / 32), so that the warp reads 32 V neighbouring floats of a
+// staged row, or of a column of the state, with one access each, and the row's q, k and g are read
+// once for all of the warp's columns.
+template <int R>
+struct RecShape {
+    static constexpr int DP = R * kRecLanes;
+    static constexpr int V = DP >= 128 ? 4 : DP / 32;
+    static constexpr int J = DP / (32 * V);
+    static constexpr int RL = V * J;
+    static_assert(DP >= 32 && DP % 32 == 0, "a staged row is at least one float per lane");
+};
+
+// p: a staged row + V lane
+template <int R>
+__device__ __forceinline__ void rec_load_rows(const float* p, float (&out)[RecShape<R>::RL]) {
+    constexpr int V = RecShape<R>::V;
 #pragma unroll
-    for (int j = 0; j < R / V; ++j) {
+    for (int j = 0; j < RecShape<R>::J; ++j) {
         if (V == 4) {
-            const float4 x = *reinterpret_cast<const float4*>(p + j * kRecLanes * V);
+            const float4 x = *reinterpret_cast<const float4*>(p + j * 32 * V);
             out[4 * j] = x.x; out[4 * j + 1] = x.y; out[4 * j + 2] = x.z; out[4 * j + 3] = x.w;
-        } else {
-            const float2 x = *reinterpret_cast<const float2*>(p + j * kRecLanes * V);
+        } else if (V == 2) {
+            const float2 x = *reinterpret_cast<const float2*>(p + j * 32 * V);
             out[2 * j] = x.x; out[2 * j + 1] = x.y;
+        } else {
+            out[j] = p[j * 32];
         }
     }
 }
 
-// The rows of one column of a state (col: the column's dk floats) that lane `sub` holds, read
-// into or written from s.  `runs`: dk is a multiple of V and the column starts on a 16-byte
-// boundary, so a run of V rows is one access.
-template <int R, int V, bool STORE>
-__device__ __forceinline__ void rec_state_rows(float* col, float (&s)[R], int sub, int dk, bool live,
-                                               bool runs) {
+// The rows of one column of a state (col: the column's dk floats) that `lane` holds, read into or
+// written from s.  `runs`: dk is a multiple of V and the column starts on a 16-byte boundary, so
+// a run of V rows is one access.
+template <int R, bool STORE>
+__device__ __forceinline__ void rec_state_rows(float* col, float (&s)[RecShape<R>::RL], int lane, int dk,
+                                               bool live, bool runs) {
+    constexpr int V = RecShape<R>::V;
 #pragma unroll
-    for (int j = 0; j < R / V; ++j) {
-        const int row = kRecLanes * V * j + V * sub;
-        if (runs) {
+    for (int j = 0; j < RecShape<R>::J; ++j) {
+        const int row = 32 * V * j + V * lane;
+        if (runs && V > 1) {
             const bool in = live && row < dk;
             if (V == 4) {
                 float4* p = reinterpret_cast<float4*>(col + row);
@@ -292,8 +309,34 @@ __device__ __forceinline__ void rec_state_rows(float* col, float (&s)[R], int su
     }
 }
 
+// Four sums over the warp in six exchanges: lanes with bit 4 clear take columns 0 and 1 from
+// their partner 16 away and give 2 and 3, then bit 3 halves the pair, then three butterfly steps.
+// Every lane returns the warp's sum of d[2 * (lane bit 4) + (lane bit 3)]; the order of the
+// additions is fixed.
+__device__ __forceinline__ float rec_reduce4(const float (&d)[4], int lane) {
+    const bool hi = (lane & 16) != 0, mid = (lane & 8) != 0;
+    float a0 = hi ? d[2] : d[0], a1 = hi ? d[3] : d[1];
+    a0 += __shfl_xor_sync(0xffffffffu, hi ? d[0] : d[2], 16);
+    a1 += __shfl_xor_sync(0xffffffffu, hi ? d[1] : d[3], 16);
+    float b = mid ? a1 : a0;
+    b += __shfl_xor_sync(0xffffffffu, mid ? a0 : a1, 8);
+    b += __shfl_xor_sync(0xffffffffu, b, 4);
+    b += __shfl_xor_sync(0xffffffffu, b, 2);
+    b += __shfl_xor_sync(0xffffffffu, b, 1);
+    return b;
+}
+
+// The reverse: every lane holds the value of column 2 * (bit 4) + (bit 3); all get all four.
+__device__ __forceinline__ void rec_gather4(float mine, int lane, float (&u)[4]) {
+    const bool hi = (lane & 16) != 0, mid = (lane & 8) != 0;
+    const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+    const float p0 = mid ? other : mine, p1 = mid ? mine : other;      // columns 2 hi, 2 hi + 1
+    const float x0 = __shfl_xor_sync(0xffffffffu, p0, 16), x1 = __shfl_xor_sync(0xffffffffu, p1, 16);
+    u[0] = hi ? x0 : p0; u[1] = hi ? x1 : p1; u[2] = hi ? p0 : x0; u[3] = hi ? p1 : x1;
+}
+
 template <typename T, int R, bool DELTA, int B>
-__global__ void __launch_bounds__(kRecThreads, (B == kRecBlockShort && R <= 16) ? 4 : 1)
+__global__ void __launch_bounds__(kRecThreads, R > 16 ? 1 : (B == kRecBlockShort ? 4 : 2))
 matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const void* __restrict__ v,
                          int vb_dtype, long long q_stride, long long k_stride, long long v_stride,
                          int act_silu, int unit, float unit_eps, float q_scale,
@@ -305,10 +348,11 @@ matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const
                          float* __restrict__ y, int heads, int qk_heads, int dk, int dv) {
     constexpr int DP = R * kRecLanes;                    // padded key width
     constexpr int PL = (DP + 31) / 32;                   // key channels a staging lane holds
-    constexpr int V = R >= 4 ? 4 : R;                    // rows a state lane reads in one load
+    constexpr int V = RecShape<R>::V, RL = RecShape<R>::RL;
     constexpr int kRowsPerLoader = B / kRecLoaders;
     constexpr int kValueLoads = (B * kRecCols + kRecLoaders * 32 - 1) / (kRecLoaders * 32);
     static_assert(B % kRecLoaders == 0, "a loader warp stages whole rows");
+    static_assert(kRecColsPerWarp == 4, "the sums over the warp are taken four at a time");
     extern __shared__ __align__(16) float rec_smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -403,16 +447,19 @@ matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const
     };
 
     // ---- the four state warps
-    const int sub = lane % kRecLanes;
-    const int col_local = (warp % kRecWarps) * kRecColsPerWarp + lane / kRecLanes;
-    const int col = blockIdx.z * kRecCols + col_local;
-    // a head's matrix is stored column by column ([dv][dk]): the 8 lanes of a column read
-    // neighbouring runs of one line
+    const int col0_local = (warp % kRecWarps) * kRecColsPerWarp;
+    const int col0 = blockIdx.z * kRecCols + col0_local;
+    const int mine = 2 * ((lane >> 4) & 1) + ((lane >> 3) & 1);   // the column whose sums this lane gets
+    // a head's matrix is stored column by column ([dv][dk]): a warp reads a column as one line
     float* st = state + (static_cast<size_t>(state_slot[r]) * heads + h) * dk * dv
-        + static_cast<size_t>(col) * dk;
+        + static_cast<size_t>(col0) * dk;
     const bool runs = dk % V == 0 && (reinterpret_cast<uintptr_t>(state) & 15) == 0;
-    float s[R];
-    if (!loader) rec_state_rows<R, V, false>(st, s, sub, dk, col < dv, runs);
+    float s[kRecColsPerWarp][RL];
+    if (!loader) {
+#pragma unroll
+        for (int c = 0; c < kRecColsPerWarp; ++c)
+            rec_state_rows<R, false>(st + static_cast<size_t>(c) * dk, s[c], lane, dk, col0 + c < dv, runs);
+    }
     auto advance = [&](int blk) {
         const float* buf = rec_smem + (blk & 1) * rec_buffer_floats(B, DP);
         const float* q_s = buf;
@@ -423,34 +470,40 @@ matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const
         const int t0 = first + blk * B;
         const int n_tok = min(B, last - t0);
         for (int tok = 0; tok < n_tok; ++tok) {
-            float kk[R], xx[R];
-            rec_load_rows<R, V>(g_s + tok * DP + sub * V, xx);
-            rec_load_rows<R, V>(k_s + tok * DP + sub * V, kk);
-            float dot[4] = {0.f, 0.f, 0.f, 0.f};
+            float kk[RL], xx[RL], d[4], u[4];
+            rec_load_rows<R>(g_s + tok * DP + lane * V, xx);
+            rec_load_rows<R>(k_s + tok * DP + lane * V, kk);
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-                s[i] *= xx[i];
-                if (DELTA) dot[i % 4] = fmaf(s[i], kk[i], dot[i % 4]);
+            for (int c = 0; c < kRecColsPerWarp; ++c) {
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < RL; ++i) {
+                    s[c][i] *= xx[i];
+                    if (DELTA) acc = fmaf(s[c][i], kk[i], acc);
+                }
+                d[c] = acc;
             }
-            float u = v_s[tok * kRecCols + col_local];
             if (DELTA) {
-                float d = (dot[0] + dot[1]) + (dot[2] + dot[3]);
-#pragma unroll
-                for (int o = kRecLanes / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-                u = b_s[tok] * (u - d);
+                const float dot = rec_reduce4(d, lane);
+                rec_gather4(b_s[tok] * (v_s[tok * kRecCols + col0_local + mine] - dot), lane, u);
+            } else {
+                const float4 x = *reinterpret_cast<const float4*>(v_s + tok * kRecCols + col0_local);
+                u[0] = x.x; u[1] = x.y; u[2] = x.z; u[3] = x.w;
             }
-            rec_load_rows<R, V>(q_s + tok * DP + sub * V, xx);
-            float out[4] = {0.f, 0.f, 0.f, 0.f};
+            rec_load_rows<R>(q_s + tok * DP + lane * V, xx);
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-                s[i] = fmaf(kk[i], u, s[i]);
-                out[i % 4] = fmaf(s[i], xx[i], out[i % 4]);
+            for (int c = 0; c < kRecColsPerWarp; ++c) {
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < RL; ++i) {
+                    s[c][i] = fmaf(kk[i], u[c], s[c][i]);
+                    acc = fmaf(s[c][i], xx[i], acc);
+                }
+                d[c] = acc;
             }
-            float o_sum = (out[0] + out[1]) + (out[2] + out[3]);
-#pragma unroll
-            for (int o = kRecLanes / 2; o > 0; o >>= 1) o_sum += __shfl_xor_sync(0xffffffffu, o_sum, o);
-            if (sub == 0 && col < dv)
-                y[static_cast<size_t>(t0 + tok) * heads * dv + static_cast<size_t>(h) * dv + col] = o_sum;
+            const float o_sum = rec_reduce4(d, lane);
+            if ((lane & 7) == 0 && col0 + mine < dv)
+                y[static_cast<size_t>(t0 + tok) * heads * dv + static_cast<size_t>(h) * dv + col0 + mine] = o_sum;
         }
     };
 
@@ -464,7 +517,11 @@ matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const
         }
         __syncthreads();                                   // block blk + 1 is staged, block blk is read
     }
-    if (!loader) rec_state_rows<R, V, true>(st, s, sub, dk, col < dv, runs);
+    if (!loader) {
+#pragma unroll
+        for (int c = 0; c < kRecColsPerWarp; ++c)
+            rec_state_rows<R, true>(st + static_cast<size_t>(c) * dk, s[c], lane, dk, col0 + c < dv, runs);
+    }
 }
 
 // ------------------------------------------- rows of a long step, made ready once
@@ -720,8 +777,7 @@ SOMI_API int somi_matrix_state_scan(const void* q, const void* k, const void* v,
     else { SOMI_LAUNCH_REC_B(TT, RR, DD, kRecBlockLong); }
 #define SOMI_REC_BY_ROWS(TT, DD)                                                                  \
     do {                                                                                          \
-        if (rows <= 2) { SOMI_LAUNCH_REC(TT, 2, DD); }                                            \
-        else if (rows <= 4) { SOMI_LAUNCH_REC(TT, 4, DD); }                                       \
+        if (rows <= 4) { SOMI_LAUNCH_REC(TT, 4, DD); }                                       \
         else if (rows <= 8) { SOMI_LAUNCH_REC(TT, 8, DD); }                                       \
         else if (rows <= 16) { SOMI_LAUNCH_REC(TT, 16, DD); }                                     \
         else { SOMI_LAUNCH_REC(TT, 32, DD); }                                                     \
