@@ -436,27 +436,46 @@ __global__ void moe_router_select_kernel(const float* __restrict__ logits, long 
 // out[t, c] = sum_k weight[t, k] * (table[t, k] < E ? y[row(t * top + k), c] : x[t, c]); float32.
 // row(e) = place[e] where the rows of y are in the grouped order, else e.  The sum runs over k in
 // ascending order.
+// A CTA per token (its entries of table, weight and place are read once by every warp); a thread
+// four neighbouring columns where the rows allow it (`vec`), else one.
 template <typename TY, typename TX>
 __global__ void moe_combine_weighted_kernel(const TY* __restrict__ y, const int* __restrict__ place,
                                             const int* __restrict__ table,
                                             const float* __restrict__ weight, const TX* __restrict__ x,
-                                            int E, int top, int H, long long n, float* __restrict__ out) {
+                                            int E, int top, int H, int T, int vec, float* __restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const long long t = i / H;
-        const int c = static_cast<int>(i - t * H);
-        float s = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const long long e = t * top + k;
-            const int expert = table[e];
-            const float v = (expert >= 0 && expert < E)
-                                ? to_float(y[(place != nullptr ? place[e] : e) * H + c])
-                                : to_float(x[i]);
-            s = fmaf(weight[e], v, s);
+    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        const long long e0 = static_cast<long long>(t) * top;
+        const TX* xr = x + static_cast<size_t>(t) * H;
+        float* o = out + static_cast<size_t>(t) * H;
+        if (vec) {
+            for (int c = 4 * threadIdx.x; c < H; c += 4 * blockDim.x) {
+                F4 s{{0.f, 0.f, 0.f, 0.f}};
+                for (int k = 0; k < top; ++k) {
+                    const int expert = table[e0 + k];
+                    const float w = weight[e0 + k];
+                    const F4 v = (expert >= 0 && expert < E)
+                        ? load4(y + static_cast<size_t>(place != nullptr ? place[e0 + k] : e0 + k) * H + c)
+                        : load4(xr + c);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) s.v[j] = fmaf(w, v.v[j], s.v[j]);
+                }
+                store4(o + c, s);
+            }
+        } else {
+            for (int c = threadIdx.x; c < H; c += blockDim.x) {
+                float s = 0.f;
+                for (int k = 0; k < top; ++k) {
+                    const int expert = table[e0 + k];
+                    const float v = (expert >= 0 && expert < E)
+                        ? to_float(y[static_cast<size_t>(place != nullptr ? place[e0 + k] : e0 + k) * H + c])
+                        : to_float(xr[c]);
+                    s = fmaf(weight[e0 + k], v, s);
+                }
+                o[c] = s;
+            }
         }
-        out[i] = s;
     }
 }
 
@@ -619,12 +638,14 @@ SOMI_API int somi_moe_router_select(const float* logits, long long l_stride, con
 SOMI_API int somi_moe_combine_weighted(const void* y, int y_dtype, const int* place, const int* table,
                                        const float* weight, const void* x, int x_dtype, int E, int top,
                                        int T, int H, float* out, cudaStream_t stream) {
-    const long long n = static_cast<long long>(T) * H;
-    if (n <= 0) return 0;
-    const int blocks = static_cast<int>(((n + 255) / 256) < 148LL * 16 ? ((n + 255) / 256) : 148LL * 16);
+    if (T <= 0 || H <= 0) return 0;
+    const int vec = (H % 4 == 0 && ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x) |
+                                     reinterpret_cast<uintptr_t>(out)) & 15) == 0) ? 1 : 0;
+    const int threads = min(256, max(32, ((H / (vec ? 4 : 1) + 31) / 32) * 32));
+    const int blocks = min(T, 148 * 32);
 #define SOMI_LAUNCH_CW(TY, TX)                                                                    \
-    launch_pdl(moe_combine_weighted_kernel<TY, TX>, dim3(blocks), dim3(256), 0, stream,           \
-               static_cast<const TY*>(y), place, table, weight, static_cast<const TX*>(x), E, top, H, n, out)
+    launch_pdl(moe_combine_weighted_kernel<TY, TX>, dim3(blocks), dim3(threads), 0, stream,       \
+               static_cast<const TY*>(y), place, table, weight, static_cast<const TX*>(x), E, top, H, T, vec, out)
     if (y_dtype == SOMI_F32 && x_dtype == SOMI_F32) SOMI_LAUNCH_CW(float, float);
     else if (y_dtype == SOMI_F32) SOMI_LAUNCH_CW(float, __nv_bfloat16);
     else if (x_dtype == SOMI_F32) SOMI_LAUNCH_CW(__nv_bfloat16, float);

@@ -622,6 +622,48 @@ __global__ void group_rmsnorm_gate_kernel(const float* __restrict__ y, const voi
     }
 }
 
+// The same with a warp per (token, part), for parts of up to kPartWarpMax columns: a lane keeps
+// its columns (lane + 32 j) in registers between the sum and the output.
+constexpr int kPartWarpMax = 256;
+constexpr int kPartWarps = 8;
+template <typename TO>
+__global__ void __launch_bounds__(kPartWarps * 32)
+group_rmsnorm_gate_warp_kernel(const float* __restrict__ y, const void* __restrict__ gate, int g_dtype,
+                               long long g_stride, const void* __restrict__ weight, int w_dtype,
+                               int w_len, float eps, TO* __restrict__ out, int C, int groups,
+                               long long parts) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long idx = static_cast<long long>(blockIdx.x) * kPartWarps + (threadIdx.x >> 5);
+    if (idx >= parts) return;
+    const long long t = idx / groups;
+    const int part = static_cast<int>(idx - t * groups);
+    const int n = C / groups, c0 = part * n;
+    const float* yr = y + static_cast<size_t>(t) * C + c0;
+    float v[kPartWarpMax / 32];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < kPartWarpMax / 32; ++j) {
+        const int i = lane + 32 * j;
+        v[j] = i < n ? yr[i] : 0.f;
+        ss = fmaf(v[j], v[j], ss);
+    }
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / static_cast<float>(n) + eps);
+    TO* o = out + static_cast<size_t>(t) * C + c0;
+#pragma unroll
+    for (int j = 0; j < kPartWarpMax / 32; ++j) {
+        const int i = lane + 32 * j;
+        if (i < n) {
+            float z = v[j] * r * load_as_float(weight, w_dtype, (c0 + i) % w_len);
+            if (gate != nullptr)
+                z *= sigmoid32(load_as_float(gate, g_dtype, static_cast<size_t>(t) * g_stride + c0 + i));
+            o[i] = from_float<TO>(z);
+        }
+    }
+}
+
 // ------------------------------------------- half the sum of two normed rows
 // out[t] = 0.5 * (a[t] / rms(a[t]) * wa + b[t] / rms(b[t]) * wb), float32.  `a` and `b` may be
 // float32 partial sums (`*_splits` slices `*_stride` apart, added in order).  One CTA per token;
@@ -827,6 +869,19 @@ SOMI_API int somi_group_rmsnorm_gate(const float* y, const void* gate, int g_dty
     if (T <= 0) return 0;
     if (groups <= 0 || C % groups || w_len <= 0) return SOMI_ERR_UNSUPPORTED;
     const int threads = threads_for(C / groups);
+    if (C / groups <= kPartWarpMax) {                     // short parts: a warp each
+        const long long parts = static_cast<long long>(T) * groups;
+        const dim3 grid(static_cast<unsigned>((parts + kPartWarps - 1) / kPartWarps));
+        if (out_dtype == SOMI_F32)
+            launch_pdl(group_rmsnorm_gate_warp_kernel<float>, grid, dim3(kPartWarps * 32), 0, stream, y,
+                       gate, g_dtype, g_stride, weight, w_dtype, w_len, eps, static_cast<float*>(out), C,
+                       groups, parts);
+        else
+            launch_pdl(group_rmsnorm_gate_warp_kernel<__nv_bfloat16>, grid, dim3(kPartWarps * 32), 0,
+                       stream, y, gate, g_dtype, g_stride, weight, w_dtype, w_len, eps,
+                       static_cast<__nv_bfloat16*>(out), C, groups, parts);
+        return launch_status();
+    }
     if (out_dtype == SOMI_F32)
         launch_pdl(group_rmsnorm_gate_kernel<float>, dim3(T, groups), dim3(threads), 0, stream, y, gate,
                    g_dtype, g_stride, weight, w_dtype, w_len, eps, static_cast<float*>(out), C, groups);
