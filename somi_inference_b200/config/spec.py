@@ -59,11 +59,14 @@ class RunSpec:
     is the index, in the schedule, of an earlier run whose cache this run reads
     without writing.  `add_embedding`: the embedding's output (the residual stream as it was
     before the first run) is added to the stream once more right in front of this run.
+    `remix`: the name of one of the model's `stream_parts`; right in front of this run the
+    stream is replaced by what that part makes of the stream and the embedding's output.
     """
 
     layer: int
     cache_of: int | None = None
     add_embedding: bool = False
+    remix: str | None = None
 
 
 @dataclass(frozen=True)
@@ -79,6 +82,8 @@ class ModelSpec:
     schedule: tuple[RunSpec, ...]
     final_norm: PartSpec
     head: PartSpec
+    # parts that act on the residual stream between runs (see `RunSpec.remix`), by name
+    stream_parts: Mapping[str, PartSpec] = field(default_factory=dict)
 
     def validate(self) -> None:
         if not self.layers:
@@ -89,6 +94,9 @@ class ModelSpec:
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"schedule[{i}] names layer {run.layer}, "
                                  f"but there are {len(self.layers)} layers")
+            if run.remix is not None and run.remix not in self.stream_parts:
+                raise ValueError(f"schedule[{i}].remix names {run.remix!r}, which is none of the "
+                                 f"model's stream parts {sorted(self.stream_parts)}")
             if run.add_embedding and i == 0:
                 raise ValueError("schedule[0] cannot add the embedding's output again")
             if run.cache_of is not None:

@@ -2,7 +2,10 @@
 // to 256, any page size: the reference kernel of the library.  Which earlier keys a token sees
 // is a parameter: all of them, the last `window`, or those of its own chunk (positions
 // i and j with i / chunk == j / chunk, chunks counted from position 0 of the sequence).  The
-// output may be multiplied by sigmoid(gate) in the epilogue.
+// output may be multiplied by sigmoid(gate) in the epilogue (a logit per output element, or with
+// `gate_per_head` one per token and head).  `softcap` > 0: a score s becomes
+// softcap * tanh(s / softcap) before the softmax.  `sinks`: a score per query head that joins the
+// softmax's denominator without a key or a value (0 gives "one more in the denominator").
 // It is the float32 path's attention and the fallback of the bfloat16 path for
 // sizes that the tensor-core kernels refuse.  Products are accumulated with
 // float32 FMAs, softmax is float32 and online, key tiles are aligned to
@@ -32,7 +35,8 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int row_stride,
                                const int* __restrict__ tiles, int n_tiles, int n_prefill_req,
                                int n_prefill_tok, int nq, int nkv, int hd, int vd, int page_size,
                                float scale, int window, int chunk, const T* __restrict__ gate,
-                               long long gate_stride, T* __restrict__ out) {
+                               long long gate_stride, int gate_per_head, float softcap,
+                               const float* __restrict__ sinks, T* __restrict__ out) {
     extern __shared__ float smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -107,6 +111,7 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int row_stride,
                 const float* q = Qs + m * hd;
                 const float* k = Ks + n * (hd + 1);
                 for (int d = 0; d < hd; ++d) s = fmaf(q[d], k[d], s);
+                if (softcap > 0.f) s = softcap * tanhf(s / softcap);
             }
             Ss[m * (kBN + 1) + n] = s;
         }
@@ -151,9 +156,12 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int row_stride,
         if (idx < kBM * vd) {
             const int m = idx / vd, d = idx - m * vd;
             if (m < rows) {
-                float o = acc[i] / l_s[m];
+                float den = l_s[m];
+                if (sinks != nullptr) den += expf(sinks[head] - m_s[m]);
+                float o = acc[i] / den;
                 if (gate != nullptr) {
-                    const float z = to_float(gate[static_cast<size_t>(row0 + m) * gate_stride + head * vd + d]);
+                    const float z = to_float(gate[static_cast<size_t>(row0 + m) * gate_stride +
+                                                  (gate_per_head ? head : head * vd + d)]);
                     o = o / (1.0f + expf(-z));
                 }
                 out[static_cast<size_t>(row0 + m) * (nq * vd) + head * vd + d] = from_float<T>(o);
@@ -173,7 +181,7 @@ SOMI_API int somi_paged_attention_generic(
     const int* block_table, int bt_stride, const int* cu_q, const int* ctx_len, const int* tiles,
     int n_tiles, int n_prefill_req, int n_prefill_tok, int n_decode, int nq, int nkv, int hd, int vd,
     int page_size, float scale, int window, int chunk, const void* gate, long long gate_stride,
-    void* out, cudaStream_t stream) {
+    int gate_per_head, float softcap, const float* sinks, void* out, cudaStream_t stream) {
     if (n_tiles + n_decode <= 0) return 0;
     if (hd <= 0 || hd > kMaxHd || vd <= 0 || vd > kMaxHd || nkv <= 0 || nq % nkv || page_size <= 0 ||
         (window > 0 && chunk > 0))
@@ -190,7 +198,8 @@ SOMI_API int somi_paged_attention_generic(
             static_cast<const T*>(qkv), row_stride, static_cast<const T*>(kcache),              \
             static_cast<const T*>(vcache), block_table, bt_stride, cu_q, ctx_len, tiles,        \
             n_tiles, n_prefill_req, n_prefill_tok, nq, nkv, hd, vd, page_size, scale, window,   \
-            chunk, static_cast<const T*>(gate), gate_stride, static_cast<T*>(out));             \
+            chunk, static_cast<const T*>(gate), gate_stride, gate_per_head, softcap, sinks,     \
+            static_cast<T*>(out));                                                              \
     } while (0)
     if (dtype == SOMI_F32) SOMI_LAUNCH_ATT(float);
     else SOMI_LAUNCH_ATT(__nv_bfloat16);

@@ -67,7 +67,8 @@ __global__ void embed_sinusoid_layernorm_kernel(const int* __restrict__ ids,
 // r = residual[row] + g * sum_s delta[s][row], g = sigmoid(gate[row]) (1 without a gate);
 // if write_back: residual[row] = r;  out[b] = (r - mean) * rstd * weight  (rms = 1: r * rrms * weight),
 // row = rows ? rows[b] : b.  delta: [splits] partial sums `split_stride` elements apart, added in order;
-// the gate's logits may be partial sums of the same kind.
+// the gate's logits may be partial sums of the same kind.  `extra`: float32 rows [N, H] that are
+// added too, outside the gate (a second branch of the same layer).
 template <typename TD, typename TG, typename TO>
 __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
                                      int splits, long long split_stride,
@@ -75,7 +76,8 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
                                      int gate_splits, long long gate_split_stride,
                                      const void* __restrict__ weight, int weight_dtype, float eps,
                                      TO* __restrict__ out, const int* __restrict__ rows, int H,
-                                     int write_back, int rms, int vec4) {
+                                     int write_back, int rms, int vec4,
+                                     const float* __restrict__ extra) {
     extern __shared__ __align__(16) float row_buf[];
     __shared__ float scratch[33];
     pdl_launch_dependents();
@@ -83,6 +85,7 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
     const int b = blockIdx.x;
     const size_t row = rows ? static_cast<size_t>(rows[b]) : static_cast<size_t>(b);
     float* r = residual + row * H;
+    const float* x = extra ? extra + row * H : nullptr;
     const TD* d = delta ? delta + row * H : nullptr;
     const TG* g = gate ? gate + row * gate_stride : nullptr;
     TO* o = out + static_cast<size_t>(b) * H;
@@ -115,6 +118,11 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
                         }
 #pragma unroll
                         for (int e = 0; e < 4; ++e) sum.v[e] *= sigmoid_f(gg.v[e]);
+                    }
+                    if (x) {
+                        const F4 t = load4(x + i);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) sum.v[e] += t.v[e];
                     }
 #pragma unroll
                     for (int e = 0; e < 4; ++e) v[k].v[e] += sum.v[e];
@@ -164,6 +172,7 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
                 for (int sp = 1; sp < gate_splits; ++sp) gg += to_float(g[sp * gate_split_stride + i]);
                 sum *= sigmoid_f(gg);
             }
+            if (x) sum += x[i];
             v += sum;
             if (write_back) r[i] = v;
         }
@@ -463,7 +472,7 @@ SOMI_API int somi_add_layernorm(float* residual, const void* delta, int delta_dt
                                 long long gate_stride, int gate_splits, long long gate_split_stride,
                                 const void* weight, int weight_dtype, float eps,
                                 void* out, int out_dtype, const int* rows, int n_out, int H,
-                                int write_back, int rms, cudaStream_t stream) {
+                                int write_back, int rms, const float* extra, cudaStream_t stream) {
     if (n_out <= 0) return 0;
     if (delta_splits < 1 || (delta_splits > 1 && delta_dtype != SOMI_F32)) return SOMI_ERR_UNSUPPORTED;
     if (gate && !delta) return SOMI_ERR_UNSUPPORTED;
@@ -474,7 +483,9 @@ SOMI_API int somi_add_layernorm(float* residual, const void* delta, int delta_dt
     const int vec4 = (H & 3) == 0 && (gate_stride & 3) == 0 && (delta_split_stride & 3) == 0 &&
                      (gate_split_stride & 3) == 0 &&
                      ((reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(gate) |
-                       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
+                       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(weight) |
+                       reinterpret_cast<uintptr_t>(extra)) & 15) == 0;
+    if (extra != nullptr && delta == nullptr) return SOMI_ERR_UNSUPPORTED;
     // few rows (a decode step waits for this kernel): a thread per four columns, the row read
     // in one pass; many rows: fewer threads per row, more rows per SM
     int threads = row_threads(H);
@@ -489,7 +500,8 @@ SOMI_API int somi_add_layernorm(float* residual, const void* delta, int delta_dt
                    stream, residual, static_cast<const TD*>(delta), delta_splits,                \
                    delta_split_stride, static_cast<const TG*>(gate), gate_stride, gate_splits,   \
                    gate_split_stride, weight,                                                    \
-                   weight_dtype, eps, static_cast<TO*>(out), rows, H, write_back, rms, vec4);    \
+                   weight_dtype, eps, static_cast<TO*>(out), rows, H, write_back, rms, vec4,     \
+                   extra);                                                                       \
     } while (0)
     // the output is of the compute dtype; the delta and the gate are that or float32 partial sums
     if (out_dtype == SOMI_F32) {
@@ -503,6 +515,54 @@ SOMI_API int somi_add_layernorm(float* residual, const void* delta, int delta_dt
         else SOMI_LAUNCH_LN(__nv_bfloat16, float, __nv_bfloat16);
     }
 #undef SOMI_LAUNCH_LN
+    return launch_status();
+}
+
+// ------------------------------------------------ stream + pending sums, beside a second stream
+// out[t] = [residual[t] + sum_s delta[s][t] + extra[t] | tail[t]] in the compute dtype, 2 H wide:
+// the input of a product that re-mixes the stream with another one (float32 sums, one rounding).
+template <typename TD, typename TO>
+__global__ void add_concat_kernel(const float* __restrict__ residual, const TD* __restrict__ delta,
+                                  int splits, long long split_stride, const float* __restrict__ extra,
+                                  const float* __restrict__ tail, TO* __restrict__ out, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t row = blockIdx.x;
+    const float* r = residual + row * H;
+    const float* tl = tail + row * H;
+    TO* o = out + row * 2 * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = r[i];
+        if (delta != nullptr) {
+            float sum = to_float(delta[row * H + i]);
+            for (int sp = 1; sp < splits; ++sp) sum += to_float(delta[sp * split_stride + row * H + i]);
+            if (extra != nullptr) sum += extra[row * H + i];
+            v += sum;
+        }
+        o[i] = from_float<TO>(v);
+        o[H + i] = from_float<TO>(tl[i]);
+    }
+}
+
+SOMI_API int somi_add_concat(const float* residual, const void* delta, int delta_dtype, int splits,
+                             long long split_stride, const float* extra, const float* tail, void* out,
+                             int out_dtype, int T, int H, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || splits < 1 || (splits > 1 && delta_dtype != SOMI_F32) ||
+        (extra != nullptr && delta == nullptr))
+        return SOMI_ERR_UNSUPPORTED;
+    const int threads = min(256, ((H + 31) / 32) * 32);
+    if (!delta) delta_dtype = out_dtype;
+#define SOMI_LAUNCH_AC(TD, TO)                                                                   \
+    launch_pdl(add_concat_kernel<TD, TO>, dim3(T), dim3(threads), 0, stream, residual,           \
+               static_cast<const TD*>(delta), splits, split_stride, extra, tail,                 \
+               static_cast<TO*>(out), H)
+    if (out_dtype == SOMI_F32) {
+        if (delta_dtype != SOMI_F32) return SOMI_ERR_UNSUPPORTED;
+        SOMI_LAUNCH_AC(float, float);
+    } else if (delta_dtype == SOMI_F32) SOMI_LAUNCH_AC(float, __nv_bfloat16);
+    else SOMI_LAUNCH_AC(__nv_bfloat16, __nv_bfloat16);
+#undef SOMI_LAUNCH_AC
     return launch_status();
 }
 

@@ -99,6 +99,37 @@ __global__ void moe_gather_rows_kernel(const T* __restrict__ a, long long a_stri
     for (int i = threadIdx.x; i < K; i += blockDim.x) dst[i] = src[i];
 }
 
+// The activation of an expert that has no gate: 0 gelu (erf), 1 gelu (tanh), 2 silu, 3 squared relu.
+__device__ __forceinline__ float unary_act(float z, int kind) {
+    switch (kind) {
+        case 0: return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+        case 1: return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+        case 2: return z / (1.0f + expf(-z));
+        default: { const float r = fmaxf(z, 0.f); return r * r; }
+    }
+}
+
+template <typename T>
+__global__ void unary_act_kernel(const T* __restrict__ x, T* __restrict__ out, long long n, int kind) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (sizeof(T) == 2 && (n & 7) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 8; i < n;
+             i += static_cast<long long>(gridDim.x) * blockDim.x * 8) {
+            uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + i);
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                h[e] = __floats2bfloat162_rn(unary_act(__low2float(h[e]), kind), unary_act(__high2float(h[e]), kind));
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + i) = raw;
+        }
+        return;
+    }
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        out[i] = from_float<T>(unary_act(to_float(x[i]), kind));
+}
+
 // The experts' activation over a product whose columns alternate gate_j, up_j:
 // out[r, j] = g * sigmoid(alpha * g) * (u + shift), g = min(gate, limit), u = clamp(up, -limit, limit)
 // (limit = infinity, alpha = 1, shift = 0: silu(gate) * up).
@@ -142,7 +173,8 @@ __global__ void clamped_gate_up_kernel(const T* __restrict__ gu, T* __restrict__
 // grid (row blocks, entries); a warp computes two weight rows at a time (a gate row and its up
 // row, or two output rows), lanes stride over K with 16-byte loads; x of the entry sits in shared
 // memory as float32.  MODE 1: the gated activation, out [entries, N / 2] bfloat16;
-// MODE 0: out [entries, N] float32.
+// MODE 0: out [entries, N] float32; MODE 2: an activation without a gate (`act`), out [entries, N]
+// bfloat16.
 constexpr int kGemvWarps = 8;
 constexpr int kGemvRowsPerCta = 64;
 template <int MODE>
@@ -150,7 +182,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32)
 moe_gemv_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, int a_div,
                 const __nv_bfloat16* __restrict__ W, const int* __restrict__ ids,
                 const int* __restrict__ table, int top, int E, void* __restrict__ out, int N, int K,
-                float limit, float alpha, float shift) {
+                float limit, float alpha, float shift, int act) {
     extern __shared__ float xs[];                          // [K]
     pdl_launch_dependents();
     pdl_wait();
@@ -191,6 +223,10 @@ moe_gemv_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, int a_d
                 const float u = fminf(fmaxf(a1, -limit), limit);
                 static_cast<__nv_bfloat16*>(out)[static_cast<size_t>(entry) * (N / 2) + row / 2] =
                     __float2bfloat16_rn(g / (1.0f + expf(-alpha * g)) * (u + shift));
+            } else if (MODE == 2) {
+                __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(entry) * N;
+                o[row] = __float2bfloat16_rn(unary_act(a0, act));
+                if (two) o[row + 1] = __float2bfloat16_rn(unary_act(a1, act));
             } else {
                 float* o = static_cast<float*>(out) + static_cast<size_t>(entry) * N;
                 o[row] = a0;
@@ -203,6 +239,7 @@ moe_gemv_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, int a_d
 // MODE 0: out (TO) rows at `scatter` positions (or the sorted position itself), N columns.
 // MODE 1: W's rows alternate gate_j, up_j; g = min(gate, limit), u = clamp(up, -limit, limit);
 //         out[pos, j] = g * sigmoid(alpha * g) * (u + shift), N / 2 columns.
+// MODE 2: out[pos, c] = act(product), N columns (an expert without a gate).
 template <typename T, typename TO, int MODE>
 __global__ void __launch_bounds__(kMoeThreads)
 grouped_gemm_kernel(const T* __restrict__ A, long long a_stride, const int* __restrict__ gather,
@@ -210,7 +247,7 @@ grouped_gemm_kernel(const T* __restrict__ A, long long a_stride, const int* __re
                     const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                     const int* __restrict__ n_tiles, int n_rows_single, TO* __restrict__ out,
                     long long out_stride, const int* __restrict__ scatter, int N, int K, float limit,
-                    float alpha, float shift) {
+                    float alpha, float shift, int act) {
     __shared__ float As[kMoeBK][kMoeBM + 1];
     __shared__ float Ws[kMoeBK][kMoeBN + 1];
     __shared__ int rows_s[kMoeBM];
@@ -283,6 +320,12 @@ grouped_gemm_kernel(const T* __restrict__ A, long long a_stride, const int* __re
                 const int c = col0 + tx * 4 + j;
                 if (c < N) out[dst + c] = from_float<TO>(acc[i][j]);
             }
+        } else if (MODE == 2) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = col0 + tx * 4 + j;
+                if (c < N) out[static_cast<size_t>(pos) * out_stride + c] = from_float<TO>(unary_act(acc[i][j], act));
+            }
         } else {
 #pragma unroll
             for (int j = 0; j < 4; j += 2) {
@@ -351,11 +394,12 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
 // the n outputs form `count` equal groups of neighbours, a group's score is its largest choice, and
 // only members of the `keep` best groups can be chosen (count <= 1: all can); the `top` largest
 // choices among those are written to chosen[t, 0..top) in falling order, their s to weight[t, ..].
-// Equal values go to the lower index.
+// Equal values go to the lower index.  With `over_chosen` the choice is made on the logits
+// themselves (no correction, no groups) and the weights are the softmax over the chosen logits only.
 __global__ void moe_router_select_kernel(const float* __restrict__ logits, long long l_stride,
                                          const float* __restrict__ correction, int n, int count,
                                          int keep, int top, int* __restrict__ chosen,
-                                         float* __restrict__ weight, int T) {
+                                         float* __restrict__ weight, int T, int over_chosen) {
     extern __shared__ float rs[];            // per warp: s [n], choice [n], group score [count]
     pdl_launch_dependents();
     pdl_wait();
@@ -380,7 +424,7 @@ __global__ void moe_router_select_kernel(const float* __restrict__ logits, long 
     for (int i = lane; i < n; i += 32) {
         const float p = sv[i] / sum;
         sv[i] = p;
-        cv[i] = correction != nullptr ? p + correction[i] : p;
+        cv[i] = over_chosen ? z[i] : (correction != nullptr ? p + correction[i] : p);
     }
     __syncwarp();
     if (count > 1 && keep < count) {
@@ -430,6 +474,14 @@ __global__ void moe_router_select_kernel(const float* __restrict__ logits, long 
             cv[arg] = NAN;                    // taken: not chosen again
         }
         __syncwarp();
+    }
+    if (over_chosen && lane == 0) {           // the first chosen has the largest logit
+        int* c = chosen + static_cast<size_t>(t) * top;
+        float* w = weight + static_cast<size_t>(t) * top;
+        const float zmax = z[c[0]];
+        float den = 0.f;
+        for (int k = 0; k < top; ++k) { w[k] = expf(z[c[k]] - zmax); den += w[k]; }
+        for (int k = 0; k < top; ++k) w[k] /= den;
     }
 }
 
@@ -533,11 +585,25 @@ SOMI_API int somi_clamped_gate_up(const void* gu, void* out, int dtype, long lon
     return launch_status();
 }
 
+SOMI_API int somi_unary_act(const void* x, void* out, int dtype, long long n, int kind,
+                            cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (kind < 0 || kind > 3) return SOMI_ERR_UNSUPPORTED;
+    const int blocks = static_cast<int>(((n + 255) / 256) < 148LL * 16 ? ((n + 255) / 256) : 148LL * 16);
+    if (dtype == SOMI_F32)
+        launch_pdl(unary_act_kernel<float>, dim3(blocks), dim3(256), 0, stream,
+                   static_cast<const float*>(x), static_cast<float*>(out), n, kind);
+    else
+        launch_pdl(unary_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                   static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), n, kind);
+    return launch_status();
+}
+
 // bfloat16, K a multiple of 8: mode 1 the gated activation (out bfloat16 [entries, N / 2]), mode 0
 // float32 rows [entries, N].  Row e of A is a[e / a_div].
 SOMI_API int somi_moe_gemv(const void* A, long long a_stride, int a_div, const void* W, const int* ids,
                            const int* table, int top, int E, int n_entries, void* out, int N, int K,
-                           int mode, float limit, float alpha, float shift, cudaStream_t stream) {
+                           int mode, float limit, float alpha, float shift, int act, cudaStream_t stream) {
     if (n_entries <= 0) return 0;
     if (K <= 0 || (K & 7) || N <= 0 || (mode == 1 && (N & 1)) || K > 40 * 1024 ||
         (reinterpret_cast<uintptr_t>(W) & 15))
@@ -549,13 +615,19 @@ SOMI_API int somi_moe_gemv(const void* A, long long a_stride, int a_div, const v
             cudaFuncSetAttribute(moe_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         launch_pdl(moe_gemv_kernel<1>, grid, dim3(kGemvWarps * 32), smem, stream,
                    static_cast<const __nv_bfloat16*>(A), a_stride, a_div,
-                   static_cast<const __nv_bfloat16*>(W), ids, table, top, E, out, N, K, limit, alpha, shift);
+                   static_cast<const __nv_bfloat16*>(W), ids, table, top, E, out, N, K, limit, alpha, shift, act);
+    } else if (mode == 2) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(moe_gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_pdl(moe_gemv_kernel<2>, grid, dim3(kGemvWarps * 32), smem, stream,
+                   static_cast<const __nv_bfloat16*>(A), a_stride, a_div,
+                   static_cast<const __nv_bfloat16*>(W), ids, table, top, E, out, N, K, limit, alpha, shift, act);
     } else {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(moe_gemv_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         launch_pdl(moe_gemv_kernel<0>, grid, dim3(kGemvWarps * 32), smem, stream,
                    static_cast<const __nv_bfloat16*>(A), a_stride, a_div,
-                   static_cast<const __nv_bfloat16*>(W), ids, table, top, E, out, N, K, limit, alpha, shift);
+                   static_cast<const __nv_bfloat16*>(W), ids, table, top, E, out, N, K, limit, alpha, shift, act);
     }
     return launch_status();
 }
@@ -567,7 +639,7 @@ SOMI_API int somi_grouped_gemm(const void* A, int dtype, long long a_stride, int
                                int use_gather, const void* W, const int* work, int E, int n_entries,
                                int max_tiles, int n_rows, void* out, int out_f32,
                                long long out_stride, int use_scatter, int N, int K, int mode,
-                               float limit, float alpha, float shift, cudaStream_t stream) {
+                               float limit, float alpha, float shift, int act, cudaStream_t stream) {
     if (N <= 0 || K <= 0) return SOMI_ERR_UNSUPPORTED;
     const int* offsets = nullptr; const int* sorted = nullptr; const int* tile_expert = nullptr;
     const int* tile_row0 = nullptr; const int* n_tiles = nullptr;
@@ -591,12 +663,14 @@ SOMI_API int somi_grouped_gemm(const void* A, int dtype, long long a_stride, int
     launch_pdl(grouped_gemm_kernel<TT, TO, MODE>, grid, dim3(kMoeThreads), 0, stream,            \
                static_cast<const TT*>(A), a_stride, gather, gather_div, static_cast<const TT*>(W), \
                offsets, tile_expert, tile_row0, n_tiles, n_rows, static_cast<TO*>(out), out_stride, \
-               scatter, N, K, limit, alpha, shift)
+               scatter, N, K, limit, alpha, shift, act)
     if (dtype == SOMI_F32) {
         if (mode == 1) SOMI_LAUNCH_GG(float, float, 1);
+        else if (mode == 2) SOMI_LAUNCH_GG(float, float, 2);
         else SOMI_LAUNCH_GG(float, float, 0);
     } else {
         if (mode == 1) SOMI_LAUNCH_GG(__nv_bfloat16, __nv_bfloat16, 1);
+        else if (mode == 2) SOMI_LAUNCH_GG(__nv_bfloat16, __nv_bfloat16, 2);
         else if (out_f32) SOMI_LAUNCH_GG(__nv_bfloat16, float, 0);
         else SOMI_LAUNCH_GG(__nv_bfloat16, __nv_bfloat16, 0);
     }
@@ -621,7 +695,7 @@ SOMI_API int somi_moe_combine(const void* y, int y_dtype, const int* place, cons
 // logits: float32 [T, l_stride] (n columns read); chosen int32 [T, top], weight float32 [T, top].
 SOMI_API int somi_moe_router_select(const float* logits, long long l_stride, const float* correction,
                                     int T, int n, int count, int keep, int top, int* chosen,
-                                    float* weight, cudaStream_t stream) {
+                                    float* weight, int over_chosen, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (n <= 0 || n > 4096 || top <= 0 || top > n || (count > 1 && (n % count || keep <= 0 || keep > count)))
         return SOMI_ERR_UNSUPPORTED;
@@ -631,7 +705,7 @@ SOMI_API int somi_moe_router_select(const float* logits, long long l_stride, con
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(moe_router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(moe_router_select_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), smem, stream,
-               logits, l_stride, correction, n, count, keep, top, chosen, weight, T);
+               logits, l_stride, correction, n, count, keep, top, chosen, weight, T, over_chosen);
     return launch_status();
 }
 

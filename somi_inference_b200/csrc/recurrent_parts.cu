@@ -138,8 +138,8 @@ __global__ void add_scaled_rmsnorm_kernel(float* __restrict__ residual, const vo
 // `vd` elements.  Every query and key head is divided by its root mean square over hd (eps inside
 // the root) and multiplied by `q_w` / `k_w` (hd elements, shared by the heads; null: no norm);
 // then entry i < rot/2 and entry i + rot/2 of the token at position p turn by p * inv_freq[i]
-// (the angle is formed and reduced in float64, its sine and cosine are float32); entries from
-// `rot` on pass.  Queries are written back in place; keys and values go to their cache slots.
+// (the angle is formed and reduced in float64, its sine and cosine are float32 and are both
+// multiplied by `magnitude`, 1 for a plain rotation); entries from `rot` on pass.  Queries are written back in place; keys and values go to their cache slots.
 // One warp per head; the normed head passes through shared memory so that a lane finds its partner.
 template <typename T>
 __global__ void headnorm_rotary_store_kernel(T* __restrict__ qkv, long long stride,
@@ -147,6 +147,7 @@ __global__ void headnorm_rotary_store_kernel(T* __restrict__ qkv, long long stri
                                              const double* __restrict__ inv_freq, int nq, int nkv,
                                              int hd, int vd, int rot, const void* __restrict__ q_w,
                                              const void* __restrict__ k_w, int w_dtype, float eps,
+                                             float magnitude,
                                              const int* __restrict__ slot_map, T* __restrict__ kcache,
                                              T* __restrict__ vcache, int page_size) {
     extern __shared__ float heads_s[];                 // [warps][hd]
@@ -187,6 +188,8 @@ __global__ void headnorm_rotary_store_kernel(T* __restrict__ qkv, long long stri
                     angle -= 6.283185307179586476925286766559 * rint(angle * 0.15915494309189533576888376337251);
                     float sn, cs;
                     sincosf(static_cast<float>(angle), &sn, &cs);
+                    sn *= magnitude;
+                    cs *= magnitude;
                     v = e < half ? fmaf(v, cs, -(mine[e + half] * sn)) : fmaf(v, cs, mine[e - half] * sn);
                 }
                 dst[e] = from_float<T>(v);
@@ -213,7 +216,7 @@ __global__ void headnorm_rotary_store_kernel(T* __restrict__ qkv, long long stri
 //     S <- S + k u^T;   y[t, h, :] = S^T q.
 // q and k of head h are head h / (heads / qk_heads) of their tensors.  With `act_silu` q and k
 // (bit 0) and v (bit 1) pass SiLU as they are read; with `unit` q and k are divided by
-// sqrt(sum of squares + unit_eps) and q is multiplied by q_scale.  v and beta are read by their
+// sqrt(sum of squares + unit_eps); q is multiplied by q_scale either way.  v and beta are read by their
 // own dtype code; with `decay_ready` a holds the decays g themselves.
 // A CTA owns kRecCols columns of S for one (request, head) and walks through the request's rows
 // of this step, B rows at a time (16, or 4 when no request has more rows than that).  Four warps
@@ -425,7 +428,7 @@ matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const
                 sq = fmaf(qv[m][j], qv[m][j], sq);
                 sk = fmaf(kv[m][j], kv[m][j], sk);
             }
-            float rq = 1.f, rk = 1.f;
+            float rq = q_scale, rk = 1.f;
             if (unit) {                                    // the sum over the head in lane order
                 sq = warp_sum(sq);
                 sk = warp_sum(sk);
@@ -436,7 +439,7 @@ matrix_state_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const
             for (int j = 0; j < PL; ++j) {
                 const int i = lane + 32 * j;
                 if (i < DP) {
-                    q_s[tok * DP + i] = unit ? qv[m][j] * rq : qv[m][j];
+                    q_s[tok * DP + i] = qv[m][j] * rq;
                     k_s[tok * DP + i] = unit ? kv[m][j] * rk : kv[m][j];
                     g_s[tok * DP + i] = (channel_decay && i < dk)
                         ? (decay_ready ? av[m][j] : expf(-rate * softplus32(av[m][j] + bias[j])))
@@ -577,7 +580,7 @@ matrix_state_prepare_kernel(const T* __restrict__ q, const T* __restrict__ k, lo
         sq = fmaf(qv[j], qv[j], sq);
         sk = fmaf(kv[j], kv[j], sk);
     }
-    float rq = 1.f, rk = 1.f;
+    float rq = q_scale, rk = 1.f;
     if (unit) {
         sq = warp_sum(sq);
         sk = warp_sum(sk);
@@ -589,7 +592,7 @@ matrix_state_prepare_kernel(const T* __restrict__ q, const T* __restrict__ k, lo
         const int i = lane + 32 * j;
         if (i < dk) {
             const size_t c = row * qk_heads * dk + static_cast<size_t>(qkh) * dk + i;
-            qn[c] = unit ? qv[j] * rq : qv[j];
+            qn[c] = qv[j] * rq;
             kn[c] = unit ? kv[j] * rk : kv[j];
         }
     }
@@ -598,12 +601,13 @@ matrix_state_prepare_kernel(const T* __restrict__ q, const T* __restrict__ k, lo
 // ------------------------------------------- RMS norm in parts, weight, sigmoid gate
 // The C columns of y[t] in `groups` equal parts of n = C / groups, each divided by its own root
 // mean square; out = that * weight[c % w_len] * sigmoid(gate[t, c]) (gate null: no gate; its rows
-// lie `g_stride` elements apart).  One CTA per (token, part).
+// lie `g_stride` elements apart; gate_act 1: SiLU of the gate instead of its sigmoid).  One CTA per (token, part).
 template <typename TO>
 __global__ void group_rmsnorm_gate_kernel(const float* __restrict__ y, const void* __restrict__ gate,
                                           int g_dtype, long long g_stride,
                                           const void* __restrict__ weight, int w_dtype, int w_len,
-                                          float eps, TO* __restrict__ out, int C, int groups) {
+                                          float eps, TO* __restrict__ out, int C, int groups,
+                                          int gate_act) {
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
@@ -617,7 +621,10 @@ __global__ void group_rmsnorm_gate_kernel(const float* __restrict__ y, const voi
     TO* o = out + static_cast<size_t>(t) * C + c0;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float v = yr[i] * r * load_as_float(weight, w_dtype, (c0 + i) % w_len);
-        if (gate != nullptr) v *= sigmoid32(load_as_float(gate, g_dtype, static_cast<size_t>(t) * g_stride + c0 + i));
+        if (gate != nullptr) {
+            const float g = load_as_float(gate, g_dtype, static_cast<size_t>(t) * g_stride + c0 + i);
+            v *= gate_act == 1 ? silu32(g) : sigmoid32(g);
+        }
         o[i] = from_float<TO>(v);
     }
 }
@@ -631,7 +638,7 @@ __global__ void __launch_bounds__(kPartWarps * 32)
 group_rmsnorm_gate_warp_kernel(const float* __restrict__ y, const void* __restrict__ gate, int g_dtype,
                                long long g_stride, const void* __restrict__ weight, int w_dtype,
                                int w_len, float eps, TO* __restrict__ out, int C, int groups,
-                               long long parts) {
+                               long long parts, int gate_act) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -657,8 +664,10 @@ group_rmsnorm_gate_warp_kernel(const float* __restrict__ y, const void* __restri
         const int i = lane + 32 * j;
         if (i < n) {
             float z = v[j] * r * load_as_float(weight, w_dtype, (c0 + i) % w_len);
-            if (gate != nullptr)
-                z *= sigmoid32(load_as_float(gate, g_dtype, static_cast<size_t>(t) * g_stride + c0 + i));
+            if (gate != nullptr) {
+                const float g = load_as_float(gate, g_dtype, static_cast<size_t>(t) * g_stride + c0 + i);
+                z *= gate_act == 1 ? silu32(g) : sigmoid32(g);
+            }
             o[i] = from_float<TO>(z);
         }
     }
@@ -758,8 +767,8 @@ SOMI_API int somi_add_scaled_rmsnorm(float* residual, const void* a, int a_dtype
 SOMI_API int somi_headnorm_rotary_store(void* qkv, int dtype, long long stride, const int* positions,
                                         const double* inv_freq, int T, int nq, int nkv, int hd, int vd,
                                         int rot, const void* q_w, const void* k_w, int w_dtype,
-                                        float eps, const int* slot_map, void* kcache, void* vcache,
-                                        int page_size, cudaStream_t stream) {
+                                        float eps, float magnitude, const int* slot_map, void* kcache,
+                                        void* vcache, int page_size, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (hd <= 0 || hd > 1024 || vd <= 0 || rot < 0 || rot > hd || (rot & 1) || nq <= 0 || nkv <= 0)
         return SOMI_ERR_UNSUPPORTED;
@@ -769,12 +778,12 @@ SOMI_API int somi_headnorm_rotary_store(void* qkv, int dtype, long long stride, 
     if (dtype == SOMI_F32)
         launch_pdl(headnorm_rotary_store_kernel<float>, grid, dim3(32 * warps), smem, stream,
                    static_cast<float*>(qkv), stride, positions, inv_freq, nq, nkv, hd, vd, rot, q_w,
-                   k_w, w_dtype, eps, slot_map, static_cast<float*>(kcache),
+                   k_w, w_dtype, eps, magnitude, slot_map, static_cast<float*>(kcache),
                    static_cast<float*>(vcache), page_size);
     else
         launch_pdl(headnorm_rotary_store_kernel<__nv_bfloat16>, grid, dim3(32 * warps), smem, stream,
                    static_cast<__nv_bfloat16*>(qkv), stride, positions, inv_freq, nq, nkv, hd, vd,
-                   rot, q_w, k_w, w_dtype, eps, slot_map, static_cast<__nv_bfloat16*>(kcache),
+                   rot, q_w, k_w, w_dtype, eps, magnitude, slot_map, static_cast<__nv_bfloat16*>(kcache),
                    static_cast<__nv_bfloat16*>(vcache), page_size);
     return launch_status();
 }
@@ -865,7 +874,8 @@ SOMI_API int somi_matrix_state_prepare(const void* q, const void* k, int dtype, 
 
 SOMI_API int somi_group_rmsnorm_gate(const float* y, const void* gate, int g_dtype, long long g_stride,
                                      const void* weight, int w_dtype, int w_len, float eps, void* out,
-                                     int out_dtype, int T, int C, int groups, cudaStream_t stream) {
+                                     int out_dtype, int T, int C, int groups, int gate_act,
+                                     cudaStream_t stream) {
     if (T <= 0) return 0;
     if (groups <= 0 || C % groups || w_len <= 0) return SOMI_ERR_UNSUPPORTED;
     const int threads = threads_for(C / groups);
@@ -875,20 +885,21 @@ SOMI_API int somi_group_rmsnorm_gate(const float* y, const void* gate, int g_dty
         if (out_dtype == SOMI_F32)
             launch_pdl(group_rmsnorm_gate_warp_kernel<float>, grid, dim3(kPartWarps * 32), 0, stream, y,
                        gate, g_dtype, g_stride, weight, w_dtype, w_len, eps, static_cast<float*>(out), C,
-                       groups, parts);
+                       groups, parts, gate_act);
         else
             launch_pdl(group_rmsnorm_gate_warp_kernel<__nv_bfloat16>, grid, dim3(kPartWarps * 32), 0,
                        stream, y, gate, g_dtype, g_stride, weight, w_dtype, w_len, eps,
-                       static_cast<__nv_bfloat16*>(out), C, groups, parts);
+                       static_cast<__nv_bfloat16*>(out), C, groups, parts, gate_act);
         return launch_status();
     }
     if (out_dtype == SOMI_F32)
         launch_pdl(group_rmsnorm_gate_kernel<float>, dim3(T, groups), dim3(threads), 0, stream, y, gate,
-                   g_dtype, g_stride, weight, w_dtype, w_len, eps, static_cast<float*>(out), C, groups);
+                   g_dtype, g_stride, weight, w_dtype, w_len, eps, static_cast<float*>(out), C, groups,
+                   gate_act);
     else
         launch_pdl(group_rmsnorm_gate_kernel<__nv_bfloat16>, dim3(T, groups), dim3(threads), 0, stream,
                    y, gate, g_dtype, g_stride, weight, w_dtype, w_len, eps,
-                   static_cast<__nv_bfloat16*>(out), C, groups);
+                   static_cast<__nv_bfloat16*>(out), C, groups, gate_act);
     return launch_status();
 }
 

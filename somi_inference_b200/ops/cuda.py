@@ -290,7 +290,8 @@ class CudaOps:
         return moved, flops
 
     def paged_attention(self, qkv, kcache, vcache, batch, group, nq, nkv, hd, scale, window,
-                        out, storage=None, value_dim=None, chunk=None, gate=None) -> None:
+                        out, storage=None, value_dim=None, chunk=None, gate=None,
+                        gate_per_head=False, softcap=None, sinks=None) -> None:
         """Attention of every token of the step over the cache (keys/values already stored).
 
         In bfloat16 with head sizes 32/64/128, portions of prompts go to the tensor-core
@@ -298,7 +299,10 @@ class CudaOps:
         heads per kv head); float32 and every other size go to the generic kernel.  So do values
         of another width than the keys (`value_dim`) and a chunked mask (`chunk`: a token sees
         the earlier tokens of its own chunk of that many positions).  `gate`: logits [T, nq *
-        value width] (rows may lie further apart); the output is multiplied by their sigmoid.
+        value width] (rows may lie further apart); the output is multiplied by their sigmoid;
+        with `gate_per_head` the logits are [T, nq], one per token and head.  `softcap`: scores
+        pass cap * tanh(score / cap); `sinks`: float32 [nq] scores that join the softmax's
+        denominator without a key.  Capped scores, sinks and per-head gates run the generic kernel.
         """
         _check(qkv, kcache, vcache, out, group.block_table)
         assert kcache.dtype == qkv.dtype
@@ -307,11 +311,17 @@ class CudaOps:
         vd = int(value_dim) if value_dim else hd
         chunk = int(chunk) if chunk else 0
         if gate is not None and not (gate.is_cuda and gate.dtype == out.dtype and gate.stride(1) == 1
-                                     and gate.shape == out.shape):
-            raise KernelError("an output gate is [T, heads * value width] of the output's dtype "
-                              "with contiguous rows")
+                                     and tuple(gate.shape) == ((out.shape[0], nq) if gate_per_head
+                                                               else tuple(out.shape))):
+            raise KernelError("an output gate is [T, heads * value width] (or [T, heads]) of the "
+                              "output's dtype with contiguous rows")
+        cap = float(softcap) if softcap else 0.0
+        if sinks is not None:
+            _check(sinks)
+            assert sinks.dtype == torch.float32 and sinks.numel() == nq
         n_decode = batch.num_requests - batch.num_prefill_requests
-        plain = vd == hd                        # what the tensor-core kernels compute
+        # what the tensor-core kernels compute
+        plain = vd == hd and cap == 0.0 and sinks is None and not (gate is not None and gate_per_head)
         if chunk and win:
             raise KernelError("a mask is a window or a chunk, not both")
         split = plain and n_decode > 0 and self.decode_supported(nq, nkv, hd, qkv.dtype)
@@ -394,8 +404,9 @@ class CudaOps:
                 ctypes.c_int(n_generic_decode), ctypes.c_int(nq), ctypes.c_int(nkv),
                 ctypes.c_int(hd), ctypes.c_int(vd), ctypes.c_int(page_size), ctypes.c_float(scale),
                 ctypes.c_int(max(win, 0)), ctypes.c_int(chunk), _ptr(gate),
-                ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out),
-                self._stream())
+                ctypes.c_longlong(gate.stride(0) if gate is not None else 0),
+                ctypes.c_int(1 if gate_per_head else 0), ctypes.c_float(cap), _ptr(sinks),
+                _ptr(out), self._stream())
             self._done(rc, "paged_attention")
             if trace.active():
                 first = batch.num_prefill_requests if tensor_core_prefill else 0
@@ -465,15 +476,20 @@ class CudaOps:
         if trace.active():
             trace.note("embed_sinusoid_layernorm", ids.shape[0] * table.shape[1] * (table.element_size() + 4))
 
-    def add_layernorm(self, residual, delta, gate, weight, eps, out, rows=None, rms=False) -> None:
+    def add_layernorm(self, residual, delta, gate, weight, eps, out, rows=None, rms=False,
+                      extra=None) -> None:
         """residual += sigmoid(gate) * delta (float32, in place; no gate: plain sum);
         out = layernorm(residual) * weight (mean taken off; with `rms`, an RMS norm instead).
 
         `delta`: [N, H] in the compute dtype, or float32 [splits, N, H] partial sums added in
         order.  `gate`: logits [N, H] whose rows may lie further apart (a view of a wider
-        product), or float32 [splits, N, H] partial sums.  With `rows`, only those rows are produced and residual is not written."""
-        _check(residual, delta, weight, out, rows)
+        product), or float32 [splits, N, H] partial sums.  `extra`: float32 [N, H] rows that are
+        added as well, outside the gate (a second branch of the layer; needs a `delta`).  With
+        `rows`, only those rows are produced and residual is not written."""
+        _check(residual, delta, weight, out, rows, extra)
         assert residual.dtype == torch.float32
+        assert extra is None or (extra.dtype == torch.float32 and extra.shape == residual.shape
+                                 and delta is not None)
         H = residual.shape[1]
         n_out = out.shape[0]
         splits, stride = 1, 0
@@ -498,7 +514,7 @@ class CudaOps:
             ctypes.c_int(gate_splits), ctypes.c_longlong(gate_split_stride),
             _ptr(weight), _code(weight), ctypes.c_float(eps), _ptr(out), _code(out), _ptr(rows),
             ctypes.c_int(n_out), ctypes.c_int(H), ctypes.c_int(0 if rows is not None else 1),
-            ctypes.c_int(1 if rms else 0), self._stream())
+            ctypes.c_int(1 if rms else 0), _ptr(extra), self._stream())
         self._done(rc, "add_layernorm")
         if trace.active():
             n = n_out * H
@@ -507,6 +523,8 @@ class CudaOps:
                 moved += splits * n * delta.element_size()
             if gate is not None:
                 moved += gate_splits * n * gate.element_size()
+            if extra is not None:
+                moved += n * 4
             if rows is None:
                 moved += n * 4
             trace.note("add_layernorm", moved, detail=f"splits={splits}" if splits > 1 else "")
@@ -865,8 +883,10 @@ class CudaOps:
             trace.note("moe_route", 12 * T * top)
         return work, max_tiles
 
+    ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu2": 3}
+
     def grouped_product(self, a, w, *, route=None, top=1, gather=False, scatter=False,
-                        gated=None, out_float32=False) -> torch.Tensor:
+                        gated=None, out_float32=False, act=None) -> torch.Tensor:
         """Rows of `a` times the matrix of their group: w [E, N, K].
 
         `route` = (work, max_tiles) from `moe_route` (None: one group, w [1, N, K], all rows).
@@ -874,8 +894,9 @@ class CudaOps:
         writes out[entry(p)] (else out[p]).  `gated` = (limit, alpha[, shift = 1]): w's rows
         alternate gate, up and the result is g * sigmoid(alpha * g) * (u + shift) with
         g = min(gate, limit), u = clamp(up, -limit, limit), N / 2 columns wide (limit infinite,
-        alpha 1, shift 0: silu(gate) * up).  Products are float32 FMAs summed over K
-        in ascending order."""
+        alpha 1, shift 0: silu(gate) * up).  `act` (a name of `ACTIVATIONS`): the result is that
+        function of the product, N columns wide (an expert without a gate).  Products are float32
+        FMAs summed over K in ascending order."""
         _check(a, w)
         E, N, K = w.shape
         assert a.shape[1] == K and a.dtype == w.dtype
@@ -887,17 +908,20 @@ class CudaOps:
             n_entries = (work.numel() - (E + 1) - 2 * max_tiles - 1) // 2
             n_rows = n_entries
         cols = N // 2 if gated is not None else N
-        out_dtype = torch.float32 if (out_float32 and gated is None) else a.dtype
+        assert gated is None or act is None
+        out_dtype = torch.float32 if (out_float32 and gated is None and act is None) else a.dtype
         out = torch.empty((n_rows, cols), dtype=out_dtype, device=a.device)
         limit, alpha, shift = self._gated(gated)
+        mode = 1 if gated is not None else (2 if act is not None else 0)
         rc = self.lib.somi_grouped_gemm(
             _ptr(a), _code(a), ctypes.c_longlong(a.stride(0)), ctypes.c_int(top),
             ctypes.c_int(1 if gather else 0), _ptr(w), _ptr(work), ctypes.c_int(E),
             ctypes.c_int(n_entries), ctypes.c_int(max_tiles), ctypes.c_int(n_rows), _ptr(out),
             ctypes.c_int(1 if out_dtype == torch.float32 else 0), ctypes.c_longlong(cols),
             ctypes.c_int(1 if scatter else 0), ctypes.c_int(N), ctypes.c_int(K),
-            ctypes.c_int(1 if gated is not None else 0), ctypes.c_float(limit), ctypes.c_float(alpha),
-            ctypes.c_float(shift), self._stream())
+            ctypes.c_int(mode), ctypes.c_float(limit), ctypes.c_float(alpha),
+            ctypes.c_float(shift), ctypes.c_int(self.ACTIVATIONS[act] if act is not None else 0),
+            self._stream())
         self._done(rc, "grouped_product")
         if trace.active():
             trace.note("grouped_product", (min(E, n_rows) * N * K + n_rows * K) * a.element_size()
@@ -947,16 +971,54 @@ class CudaOps:
             trace.note("clamped_gate_up", 3 * out.numel() * out.element_size())
         return out
 
+    def unary_act(self, x, act: str) -> torch.Tensor:
+        """`act` (a name of `ACTIVATIONS`) of every element, float32 arithmetic."""
+        _check(x)
+        out = torch.empty_like(x)
+        rc = self.lib.somi_unary_act(_ptr(x), _ptr(out), _code(x), ctypes.c_longlong(x.numel()),
+                                     ctypes.c_int(self.ACTIVATIONS[act]), self._stream())
+        self._done(rc, "unary_act")
+        if trace.active():
+            trace.note("unary_act", 2 * x.numel() * x.element_size())
+        return out
+
+    def add_concat(self, residual, delta, extra, tail, out) -> None:
+        """out = [residual + delta + extra | tail] in out's dtype, [N, 2 H]; residual, tail and
+        extra float32 [N, H]; `delta`: [N, H], or float32 [splits, N, H] partial sums added in
+        order, or None (then there is no extra either).  Nothing but `out` is written."""
+        _check(residual, delta, extra, tail, out)
+        assert residual.dtype == tail.dtype == torch.float32 and residual.shape == tail.shape
+        assert extra is None or (extra.dtype == torch.float32 and delta is not None)
+        N, H = residual.shape
+        assert tuple(out.shape) == (N, 2 * H)
+        splits, stride = 1, 0
+        if delta is not None and delta.dim() == 3:
+            assert delta.dtype == torch.float32
+            splits, stride = delta.shape[0], delta.shape[1] * delta.shape[2]
+        rc = self.lib.somi_add_concat(
+            _ptr(residual), _ptr(delta), _code(delta) if delta is not None else _code(out),
+            ctypes.c_int(splits), ctypes.c_longlong(stride), _ptr(extra), _ptr(tail), _ptr(out),
+            _code(out), ctypes.c_int(N), ctypes.c_int(H), self._stream())
+        self._done(rc, "add_concat")
+        if trace.active():
+            moved = N * H * (8 + 2 * out.element_size())
+            if delta is not None:
+                moved += splits * N * H * delta.element_size()
+            if extra is not None:
+                moved += N * H * 4
+            trace.note("add_concat", moved)
+
     def moe_gemv_supported(self, n_entries: int, K: int, dtype) -> bool:
         """Whether a step's entries are few enough (and the sizes fit) for each to stream its
         expert's rows by itself."""
         return dtype == torch.bfloat16 and n_entries <= 64 and K % 8 == 0 and K <= 40 * 1024
 
-    def moe_gemv(self, a, w, token_ids, table, *, per_token: bool, gated=None) -> torch.Tensor:
+    def moe_gemv(self, a, w, token_ids, table, *, per_token: bool, gated=None, act=None) -> torch.Tensor:
         """A step of few tokens: entry e = (token, k) times the matrix of expert
         table[id[token], k]; w [E, N, K] bfloat16.  `per_token`: a has one row per token (else one
         per entry).  `gated` = (limit, alpha): rows of w alternate gate, up and the result is the
-        experts' activation, bfloat16 [entries, N / 2]; else float32 [entries, N]."""
+        experts' activation, bfloat16 [entries, N / 2]; `act` (a name of `ACTIVATIONS`): that
+        function of the product, bfloat16 [entries, N]; else float32 [entries, N]."""
         _check(a, w, token_ids, table)
         E, N, K = w.shape
         top = table.shape[1]
@@ -964,16 +1026,21 @@ class CudaOps:
         n = n_tokens * top
         assert a.dtype == w.dtype == torch.bfloat16 and a.shape[1] == K
         assert a.shape[0] == (n_tokens if per_token else n)
+        assert gated is None or act is None
         if gated is not None:
             out = torch.empty((n, N // 2), dtype=torch.bfloat16, device=a.device)
+        elif act is not None:
+            out = torch.empty((n, N), dtype=torch.bfloat16, device=a.device)
         else:
             out = torch.empty((n, N), dtype=torch.float32, device=a.device)
         limit, alpha, shift = self._gated(gated)
+        mode = 1 if gated is not None else (2 if act is not None else 0)
         rc = self.lib.somi_moe_gemv(
             _ptr(a), ctypes.c_longlong(a.stride(0)), ctypes.c_int(top if per_token else 1), _ptr(w),
             _ptr(token_ids), _ptr(table), ctypes.c_int(top), ctypes.c_int(E), ctypes.c_int(n),
-            _ptr(out), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(1 if gated is not None else 0),
-            ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(shift), self._stream())
+            _ptr(out), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(mode),
+            ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(shift),
+            ctypes.c_int(self.ACTIVATIONS[act] if act is not None else 0), self._stream())
         self._done(rc, "moe_gemv")
         if trace.active():
             trace.note("moe_gemv", (min(E, n) * N * K + n * K) * 2 + out.numel() * out.element_size(),
@@ -1070,11 +1137,12 @@ class CudaOps:
             trace.note("add_scaled_rmsnorm", moved)
 
     def headnorm_rotary_store(self, qkv, positions, inv_freq, nq, nkv, hd, vd, rotary_dim, q_weight,
-                              k_weight, eps, slot_map, kcache, vcache) -> None:
+                              k_weight, eps, slot_map, kcache, vcache, magnitude: float = 1.0) -> None:
         """Rows of `qkv` hold nq query heads and nkv key heads of `hd` elements, then nkv value
         heads of `vd`.  Every query and key head passes an RMS norm over the head with
         `q_weight` / `k_weight` ([hd]; None: no norm); then entry i < rotary_dim / 2 and entry
-        i + rotary_dim / 2 turn by position * inv_freq[i] (`inv_freq` float64).  Queries are
+        i + rotary_dim / 2 turn by position * inv_freq[i] (`inv_freq` float64), sine and cosine
+        both multiplied by `magnitude`.  Queries are
         rewritten in place; keys and values go to their cache slots (`slot_map` None: nothing is
         stored)."""
         _check(positions, inv_freq, slot_map, kcache, vcache, q_weight, k_weight)
@@ -1092,7 +1160,8 @@ class CudaOps:
             ctypes.c_int(qkv.shape[0]), ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd),
             ctypes.c_int(vd), ctypes.c_int(rotary_dim), _ptr(q_weight), _ptr(k_weight),
             ctypes.c_int(_code(q_weight) if q_weight is not None else _F32), ctypes.c_float(eps),
-            _ptr(slot_map), _ptr(kcache), _ptr(vcache), ctypes.c_int(page_size), self._stream())
+            ctypes.c_float(magnitude), _ptr(slot_map), _ptr(kcache), _ptr(vcache),
+            ctypes.c_int(page_size), self._stream())
         self._done(rc, "headnorm_rotary_store")
         if trace.active():
             n = qkv.shape[0] * ((nq + nkv) * hd + nkv * vd)
@@ -1118,8 +1187,8 @@ class CudaOps:
         g is `decay` [heads], or per key channel exp(-exp(a_log) * softplus(decay_logits +
         dt_bias)) (`decay_logits` float32 [T, heads * dk], rows may lie further apart).  q, k
         ([T, qk_heads * dk]) and v ([T, heads * dv]) may be views of wider rows; `act_silu`: they
-        pass SiLU as they are read; `unit_eps`: q and k are divided by sqrt(sum of squares + it)
-        and q is multiplied by `q_scale`.  y: float32 [T, heads * dv].  `prepare` (None: by the
+        pass SiLU as they are read; `unit_eps`: q and k are divided by sqrt(sum of squares + it);
+        q is multiplied by `q_scale` either way.  y: float32 [T, heads * dv].  `prepare` (None: by the
         step's longest request) only chooses where q, k and g are computed; y is the same."""
         _check(state, y, dt_bias, a_log, decay)
         for t in (q, k, v, beta, decay_logits):
@@ -1152,7 +1221,7 @@ class CudaOps:
             if trace.active():
                 trace.note("matrix_state_prepare", 2 * n * (q.element_size() + 4) + 2 * n_g * 4)
             q, k, decay_logits = qn, kn, gd
-            act, unit, ready = act & 2, 0, 1
+            act, unit, ready, q_scale = act & 2, 0, 1, 1.0      # q is scaled already
         rc = self.lib.somi_matrix_state_scan(
             _ptr(q), _ptr(k), _ptr(v), _code(q), vb_code, ctypes.c_longlong(q.stride(0)),
             ctypes.c_longlong(k.stride(0)), ctypes.c_longlong(v.stride(0)),
@@ -1176,10 +1245,10 @@ class CudaOps:
             trace.note("matrix_state_scan", moved, (8.0 if beta is not None else 5.0) * T * heads * dk * dv,
                        detail="delta rule" if beta is not None else "decayed sum")
 
-    def group_rmsnorm_gate(self, y, gate, weight, eps, groups, out) -> None:
+    def group_rmsnorm_gate(self, y, gate, weight, eps, groups, out, gate_act: str = "sigmoid") -> None:
         """out = rmsnorm over each of `groups` equal parts of y (float32), times weight (as long
         as a row, or as a part and then shared by the parts), times sigmoid(gate) where there is
-        a gate ([T, C], rows may lie further apart)."""
+        a gate ([T, C], rows may lie further apart); `gate_act` "silu": times silu(gate) instead."""
         _check(y, weight, out)
         if gate is not None and not (gate.is_cuda and gate.stride(1) == 1 and gate.shape == y.shape):
             raise KernelError("group_rmsnorm_gate takes a gate with contiguous rows")
@@ -1190,7 +1259,8 @@ class CudaOps:
             _ptr(y), _ptr(gate), ctypes.c_int(_code(gate) if gate is not None else _F32),
             ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(weight), _code(weight),
             ctypes.c_int(weight.numel()), ctypes.c_float(eps), _ptr(out), _code(out),
-            ctypes.c_int(y.shape[0]), ctypes.c_int(C), ctypes.c_int(groups), self._stream())
+            ctypes.c_int(y.shape[0]), ctypes.c_int(C), ctypes.c_int(groups),
+            ctypes.c_int({"sigmoid": 0, "silu": 1}[gate_act]), self._stream())
         self._done(rc, "group_rmsnorm_gate")
         if trace.active():
             trace.note("group_rmsnorm_gate", y.numel() * (4 + out.element_size()
@@ -1231,11 +1301,14 @@ class CudaOps:
         if trace.active():
             trace.note("relu2", 2 * x.numel() * x.element_size())
 
-    def moe_router_select(self, logits, correction, count: int, keep: int, top: int):
+    def moe_router_select(self, logits, correction, count: int, keep: int, top: int,
+                          over_chosen: bool = False):
         """logits float32 [T, n] -> (chosen int32 [T, top], weight float32 [T, top]): softmax over
         the n outputs; the choice is made on softmax + correction (None: the softmax) among the
         members of the `keep` best of `count` equal groups of neighbours (a group's score is its
-        best member's; count <= 1: no groups); the weights are the chosen outputs' softmax."""
+        best member's; count <= 1: no groups); the weights are the chosen outputs' softmax.
+        `over_chosen`: the `top` largest logits are chosen (no correction, no groups) and the
+        weights are the softmax over the chosen logits only."""
         _check(logits, correction)
         assert logits.dtype == torch.float32 and (correction is None or correction.dtype == torch.float32)
         T, n = logits.shape
@@ -1244,7 +1317,8 @@ class CudaOps:
         rc = self.lib.somi_moe_router_select(_ptr(logits), ctypes.c_longlong(logits.stride(0)),
                                              _ptr(correction), ctypes.c_int(T), ctypes.c_int(n),
                                              ctypes.c_int(count), ctypes.c_int(keep), ctypes.c_int(top),
-                                             _ptr(chosen), _ptr(weight), self._stream())
+                                             _ptr(chosen), _ptr(weight),
+                                             ctypes.c_int(1 if over_chosen else 0), self._stream())
         self._done(rc, "moe_router_select")
         if trace.active():
             trace.note("moe_router_select", T * (n * 4 + top * 8))

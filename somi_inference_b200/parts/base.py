@@ -26,9 +26,12 @@ Interfaces (duck-typed; the classes below only document them):
                  part the layer does not have is None), with a fourth argument `extras`
                  (name -> built layer extra) where the layer has some; `forward(residual,
                  pending, batch, cache, owns_cache)` returns the delta that the next norm has to
-                 add (a tensor, or a `GatedDelta` / `NormedDelta` / `ScaledBranches` for norms
-                 or arrangements that take one).  An arrangement
+                 add (a tensor, or a `GatedDelta` / `NormedDelta` / `ScaledBranches` / `BranchSum`
+                 for norms or arrangements that take one).  An arrangement
                  whose extras keep state per request answers `state_needs() -> StateNeeds`.
+* Stream part:   `forward(residual, pending, start) -> float32 [T, H]`: the stream that replaces
+                 `residual` in front of a run whose `RunSpec.remix` names the part; `pending` is
+                 what the run before left to be added (or None), `start` the embedding's output.
 * Layer extra:   whatever its arrangement calls; `declare(params)` and `__init__(params,
                  tensors, ctx)` like every part.
 """
@@ -140,6 +143,17 @@ class ScaledBranches:
     scale_b: torch.Tensor | None
     mult: float
     extra: torch.Tensor | None = None
+
+
+@dataclass
+class BranchSum:
+    """What a layer whose mixer and feed-forward read the output of one norm hands to the next
+    norm: the mixer's result ([T, H], or float32 [splits, T, H] partial sums) and the
+    feed-forward's (float32 [T, H], or None for a layer without one).  The next norm adds
+    both to the residual stream before it normalises."""
+
+    a: torch.Tensor
+    b: torch.Tensor | None = None
 
 
 def with_extra_rows(pending, rows: torch.Tensor):

@@ -9,7 +9,7 @@ while normalising, and returns its own feed-forward output as the next `pending`
 
 from __future__ import annotations
 
-from .base import GatedDelta, NormedDelta, ScaledBranches, StateNeeds
+from .base import BranchSum, GatedDelta, NormedDelta, ScaledBranches, StateNeeds
 from .registry import ARRANGEMENTS
 
 
@@ -159,3 +159,26 @@ class ParallelBranchesBlock:
         f = None if self.feed_forward is None else self.feed_forward.forward(hf, batch)
         return ScaledBranches(a, self.mixer_scale, f,
                               None if f is None else self.feed_forward_scale, self.mult)
+
+
+@ARRANGEMENTS.register("shared_norm")
+class SharedNormBlock:
+    """Mixer and feed-forward read the output of one norm, and both results join the stream:
+        h = norm(x);  x = x + mixer(h) + feed_forward(h)
+    A layer without a feed-forward has the mixer's branch only.  Norm: `shared`, of any kind whose
+    `forward` takes a `BranchSum`: the sums are made in float32 by the next norm's kernel."""
+
+    def __init__(self, mixer, feed_forward, norms) -> None:
+        if mixer is None:
+            raise ValueError("the shared-norm arrangement needs a mixer")
+        if set(norms) != {"shared"}:
+            raise ValueError(f"the shared-norm arrangement takes the norm 'shared', got {sorted(norms)}")
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.norm = norms["shared"]
+
+    def forward(self, residual, pending, batch, cache, owns_cache):
+        h = self.norm.forward(residual, pending)
+        a = self.mixer.forward(h, batch, cache, owns_cache)
+        f = None if self.feed_forward is None else self.feed_forward.forward(h, batch)
+        return BranchSum(a, f)

@@ -16,9 +16,9 @@ from __future__ import annotations
 
 import torch
 
-from .base import BuildContext, StateNeeds, TensorDecl, names_of
+from .base import BranchSum, BuildContext, StateNeeds, TensorDecl, names_of
 from .linear import Linear
-from .registry import LAYER_EXTRAS
+from .registry import LAYER_EXTRAS, STREAM_PARTS
 
 
 @LAYER_EXTRAS.register("sigmoid_gate")
@@ -90,3 +90,37 @@ class Constant:
 
     def __init__(self, params, tensors, ctx: BuildContext) -> None:
         self.value = float(params["value"])
+
+
+@STREAM_PARTS.register("embedding_remix")
+class EmbeddingRemix:
+    """A product that makes a new residual stream out of the stream and the embedding's output:
+        x <- W [x; x0]          W: [H, 2 H], the stream's columns first.
+    What the run before left pending is added to the stream first.  The sums are float32; the
+    product reads [x; x0] in the compute dtype and leaves a float32 stream."""
+
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        hidden = int(params["hidden_size"])
+        return [TensorDecl(names_of(params)["weight"], (hidden, 2 * hidden))]
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        self.ctx = ctx
+        self.hidden = int(params["hidden_size"])
+        self.proj = Linear(tensors[names_of(params)["weight"]], None, ctx.ops)
+
+    def forward(self, residual: torch.Tensor, pending, start: torch.Tensor) -> torch.Tensor:
+        delta = extra = None
+        if isinstance(pending, BranchSum):
+            delta, extra = pending.a, pending.b
+            if extra is not None and extra.dtype != torch.float32:
+                extra = extra.float()
+        elif pending is None or isinstance(pending, torch.Tensor):
+            delta = pending
+        else:
+            raise ValueError("the stream is re-mixed behind a layer that hands on a tensor or a "
+                             f"BranchSum, not {type(pending).__name__}")
+        both = torch.empty((residual.shape[0], 2 * self.hidden), dtype=self.ctx.dtype,
+                           device=residual.device)
+        self.ctx.ops.add_concat(residual, delta, extra, start, both)
+        return self.proj.to_float32(both)

@@ -7,7 +7,7 @@ With h the mixer's input, per token:
     k_h = W_uk,h c,  v_h = W_uv,h c      for every head h, from the cached c of each position
     s   = scale * q_h . k_h  over the window's positions; softmax with a sink per head in the
           denominator (a learned score without a key or value)
-    out = W_o concat_h(sum_j p_j v_h,j)
+    out = W_o (concat_h(sum_j p_j v_h,j) * sigmoid(W_g h))    (the gate only where `gate` is set)
 No position encoding acts on queries or keys.  A mixer with `own_latent` false has no W_dkv: its
 run reads the cache of an earlier run (same kv_rank) with its own W_uk, W_uv, window and sink.
 
@@ -47,6 +47,8 @@ class LatentAttentionMixer:
                      TensorDecl(n["kv_norm"], (rkv,), init="ones", matrix=False)]
         if params.get("sink"):
             decl.append(TensorDecl(n["sink"], (H,), init="zeros", matrix=False))
+        if params.get("gate"):
+            decl.append(TensorDecl(n["gate"], (H * dv, D)))
         return decl
 
     def __init__(self, params, tensors, ctx: BuildContext) -> None:
@@ -74,6 +76,7 @@ class LatentAttentionMixer:
         self.v_up = tensors[n["v_up"]].view(H, self.value_dim, self.kv_rank).contiguous()
         self.out = Linear(tensors[n["out"]], None, ctx.ops)
         self.sinks = tensors[n["sink"]].float().contiguous() if params.get("sink") else None
+        self.gate = Linear(tensors[n["gate"]], None, ctx.ops) if params.get("gate") else None
 
     def cache_needs(self) -> CacheNeeds:
         # one "head" of kv_rank elements per position, read as key and as value: no value tensor
@@ -101,5 +104,7 @@ class LatentAttentionMixer:
                              self.sinks, o_lat)
         o = ops.head_product(o_lat, self.v_up, heads_first=False)    # [T, H, value_dim]
         o = o.view(T, H * self.value_dim)
+        if self.gate is not None:
+            ops.sigmoid_gate_mul(o, self.gate(x))
         partial = self.out.partial_sums(o)
         return partial if partial is not None else self.out(o)

@@ -17,6 +17,9 @@ H heads over G query/key heads (head i reads query/key head i // (H / G)):
     M <- decay * M + k v^T;  o = M^T q
     out = Wo (rmsnorm_over_all_heads(o) * norm * sigmoid(Wg h))
 
+`gated_linear_attention` (at the end of the file): a decay per key channel and token from a
+sigmoid, no correction, a SiLU gate.
+
 Products run in the compute dtype with float32 accumulation; unit norms, beta, the decays with
 their softplus and exponentials, the recurrence, the norms and the gates' sigmoids are float32 in
 the kernels.  One kernel walks through a request's rows of the step, so a sequence may arrive
@@ -176,5 +179,79 @@ class DecaySumMixer:
                               self.key_dim, self.value_dim, act_silu=True, decay=self.decay)
         gated = torch.empty((T, self.inner), dtype=x.dtype, device=x.device)
         ops.group_rmsnorm_gate(y, proj[:, 2 * w + self.inner:], self.norm_weight, self.eps, 1, gated)
+        partial = self.out.partial_sums(gated)
+        return partial if partial is not None else self.out(gated)
+
+
+@MIXERS.register("gated_linear_attention")
+class GatedLinearAttentionMixer:
+    """Linear attention with a learned decay per key channel and token:
+
+        q = Wq h * q_scale, k = Wk h, v = Wv h                        (heads x key / value width)
+        alpha = sigmoid(Wa2 (Wa1 h) + ba)^(1 / tau)                   per head and key channel
+        M <- alpha[:, None] * M + k v^T;  o = M^T q
+        out = Wo (rmsnorm_per_head(o) * norm * silu(Wg h))            (`norm`: one head's width)
+
+    alpha = exp(-softplus(-z) / tau), which is the matrix-state kernel's channel decay
+    exp(-rate * softplus(a + bias)) with a = -z, bias = -ba and rate = 1 / tau: the second decay
+    matrix and its bias are held negated (exact in every dtype).  The decay's logits are a float32
+    product; softplus, the exponential, the recurrence, the norm and the gate's SiLU are float32."""
+
+    graph_safe = True
+    STATE = "gla_state"
+
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        n = names_of(params)
+        hidden, H = int(params["hidden_size"]), int(params["heads"])
+        d, dv, r = int(params["key_dim"]), int(params["value_dim"]), int(params["decay_rank"])
+        return [TensorDecl(n["q_weight"], (H * d, hidden)), TensorDecl(n["k_weight"], (H * d, hidden)),
+                TensorDecl(n["v_weight"], (H * dv, hidden)), TensorDecl(n["gate_weight"], (H * dv, hidden)),
+                TensorDecl(n["decay_down"], (r, hidden)), TensorDecl(n["decay_up"], (H * d, r)),
+                TensorDecl(n["decay_bias"], (H * d,), init="zeros", matrix=False),
+                TensorDecl(n["norm"], (dv,), init="ones", matrix=False),
+                TensorDecl(n["o_weight"], (hidden, H * dv))]
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        import math
+        n = names_of(params)
+        self.ctx = ctx
+        self.heads = int(params["heads"])
+        self.key_dim, self.value_dim = int(params["key_dim"]), int(params["value_dim"])
+        ctx.ops.check_matrix_state_geometry(self.heads, self.heads, self.key_dim, self.value_dim)
+        tau = float(params["tau"])
+        if not tau > 0.0:
+            raise ValueError("tau must be positive")
+        self.eps = float(params["eps"])
+        self.q_scale = float(params.get("q_scale", self.key_dim ** -0.5))
+        self.qk_width = self.heads * self.key_dim
+        self.inner = self.heads * self.value_dim
+        self.proj = Linear(torch.cat([tensors[n["q_weight"]], tensors[n["k_weight"]],
+                                      tensors[n["v_weight"]], tensors[n["gate_weight"]]], 0).contiguous(),
+                           None, ctx.ops)
+        self.narrow = Linear(tensors[n["decay_down"]], None, ctx.ops)
+        self.wide = Linear((-tensors[n["decay_up"]]).contiguous(), None, ctx.ops)
+        self.neg_bias = (-tensors[n["decay_bias"]].float()).contiguous()
+        self.log_rate = torch.full((self.heads,), -math.log(tau), dtype=torch.float32, device=ctx.device)
+        self.norm_weight = tensors[n["norm"]]
+        self.out = Linear(tensors[n["o_weight"]], None, ctx.ops)
+
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds(paged=None, state=StateNeeds(
+            {self.STATE: ((self.heads, self.value_dim, self.key_dim), torch.float32)}))
+
+    def forward(self, x: torch.Tensor, batch, cache, owns_cache: bool) -> torch.Tensor:
+        ops = self.ctx.ops
+        T, w = x.shape[0], self.qk_width
+        proj = self.proj(x)                                     # [T, q | k | v | gate logits]
+        logits = self.wide.to_float32(self.narrow(x))           # [T, heads * key]: -z
+        y = torch.empty((T, self.inner), dtype=torch.float32, device=x.device)
+        ops.matrix_state_scan(proj[:, :w], proj[:, w:2 * w], proj[:, 2 * w:2 * w + self.inner],
+                              cache.state[self.STATE], batch, y, self.heads, self.heads,
+                              self.key_dim, self.value_dim, q_scale=self.q_scale,
+                              decay_logits=logits, dt_bias=self.neg_bias, a_log=self.log_rate)
+        gated = torch.empty((T, self.inner), dtype=x.dtype, device=x.device)
+        ops.group_rmsnorm_gate(y, proj[:, 2 * w + self.inner:], self.norm_weight, self.eps,
+                               self.heads, gated, gate_act="silu")
         partial = self.out.partial_sums(gated)
         return partial if partial is not None else self.out(gated)

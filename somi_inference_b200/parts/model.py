@@ -15,7 +15,7 @@ import torch
 from ..config.spec import LayerSpec, ModelSpec
 from .base import BuildContext, CacheNeeds, StateNeeds, TensorDecl, with_extra_rows
 from .registry import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, LAYER_EXTRAS, MIXERS,
-                       NORMS)
+                       NORMS, STREAM_PARTS)
 
 
 def declared_tensors(spec: ModelSpec) -> dict[str, TensorDecl]:
@@ -38,6 +38,8 @@ def declared_tensors(spec: ModelSpec) -> dict[str, TensorDecl]:
             add(NORMS.declare(norm))
         for extra in layer.extras.values():
             add(LAYER_EXTRAS.declare(extra))
+    for part in spec.stream_parts.values():
+        add(STREAM_PARTS.declare(part))
     add(NORMS.declare(spec.final_norm))
     add(HEADS.declare(spec.head))
     return out
@@ -56,6 +58,8 @@ class Decoder:
                   if name in tensors and not d.ignored}
         self.embedding = EMBEDDINGS.build(spec.embedding, placed, ctx)
         self.layers = [self._build_layer(layer, placed) for layer in spec.layers]
+        self.stream_parts = {name: STREAM_PARTS.build(part, placed, ctx)
+                             for name, part in spec.stream_parts.items()}
         self.final_norm = NORMS.build(spec.final_norm, placed, ctx)
         self.head = HEADS.build(spec.head, placed, ctx)
         self.schedule = spec.schedule
@@ -101,10 +105,16 @@ class Decoder:
         pending = None
         # a schedule that adds the embedding's output again keeps a copy of it: the stream itself
         # is written by the norms from the first run on
-        start = residual.clone() if any(run.add_embedding for run in self.schedule) else None
+        start = (residual.clone() if any(run.add_embedding or run.remix is not None
+                                         for run in self.schedule) else None)
         for i, run in enumerate(self.schedule):
             if run.add_embedding:
                 pending = with_extra_rows(pending, start)
+            if run.remix is not None:
+                # the stream with everything added that is due, re-mixed with the embedding's
+                # output: a new stream, nothing pending
+                residual = self.stream_parts[run.remix].forward(residual, pending, start)
+                pending = None
             pending = self.layers[run.layer].forward(residual, pending, batch, cache.view(i),
                                                      run.cache_of is None)
         if batch.logit_rows.shape[0] == 0:

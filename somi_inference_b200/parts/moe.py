@@ -115,6 +115,11 @@ class RoutedMoE:
         experts without tensors: expert(h) = h
         y = sum of weight * expert(h) over the chosen
 
+    Two parameters change the form.  `weights` = "softmax_chosen": the `top` largest logits are
+    chosen (no correction, no groups) and the weights are the softmax over the chosen logits only.
+    `activation` (a name of the kernel table's `ACTIVATIONS`, e.g. "gelu"): experts without a gate,
+    expert(h) = W_down act(W_up h), and no gate tensors.
+
     The router's logits are a float32 product; one kernel makes softmax, choice and weights and
     leaves a table row per token, from which the experts run like those of `table_moe`: entry by
     entry for a step of few tokens, grouped by expert otherwise.  The weighted sum is float32."""
@@ -130,8 +135,9 @@ class RoutedMoE:
         if params.get("correction"):
             decl.append(TensorDecl(n["correction"], (outputs,), init="zeros", matrix=False))
         for e in range(E):
-            decl += [TensorDecl(n["gate"][e], (ff, hidden)), TensorDecl(n["up"][e], (ff, hidden)),
-                     TensorDecl(n["down"][e], (hidden, ff))]
+            if not params.get("activation"):
+                decl.append(TensorDecl(n["gate"][e], (ff, hidden)))
+            decl += [TensorDecl(n["up"][e], (ff, hidden)), TensorDecl(n["down"][e], (hidden, ff))]
         return decl
 
     def __init__(self, params, tensors, ctx: BuildContext) -> None:
@@ -139,6 +145,14 @@ class RoutedMoE:
         self.ctx = ctx
         self.experts, self.top = int(params["experts"]), int(params["top"])
         self.outputs = self.experts + int(params.get("identity", 0))
+        self.over_chosen = params.get("weights", "softmax_all") == "softmax_chosen"
+        if params.get("weights", "softmax_all") not in ("softmax_all", "softmax_chosen"):
+            raise ValueError(f"unknown router weights {params['weights']!r}")
+        if self.over_chosen and (params.get("correction") or params.get("groups")):
+            raise ValueError("a softmax over the chosen logits goes with no correction and no groups")
+        self.act = params.get("activation")
+        if self.act is not None and self.act not in ctx.ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {self.act!r}; known: {sorted(ctx.ops.ACTIVATIONS)}")
         groups = params.get("groups") or {}
         self.group_count = int(groups.get("count", 1))
         self.group_keep = int(groups.get("keep", self.group_count))
@@ -153,19 +167,24 @@ class RoutedMoE:
         self.correction = (tensors[n["correction"]].float().contiguous()
                            if params.get("correction") else None)
         E = range(self.experts)
-        self.w_gate_up = _interleave(torch.stack([tensors[n["gate"][e]] for e in E]),
-                                     torch.stack([tensors[n["up"][e]] for e in E])).contiguous()
+        if self.act is None:
+            self.w_gate_up = _interleave(torch.stack([tensors[n["gate"][e]] for e in E]),
+                                         torch.stack([tensors[n["up"][e]] for e in E])).contiguous()
+            self.gated = (float("inf"), 1.0, 0.0)           # silu(gate) * up
+        else:
+            self.w_gate_up = torch.stack([tensors[n["up"][e]] for e in E]).contiguous()
+            self.gated = None
         self.w_down = torch.stack([tensors[n["down"][e]] for e in E]).contiguous()
-        self.gated = (float("inf"), 1.0, 0.0)               # silu(gate) * up
 
     def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
         ops, top, E = self.ctx.ops, self.top, self.experts
         logits = self.router.to_float32(x)
         chosen, weight = ops.moe_router_select(logits, self.correction, self.group_count,
-                                               self.group_keep, top)
+                                               self.group_keep, top, over_chosen=self.over_chosen)
         n_entries = x.shape[0] * top
         if ops.moe_gemv_supported(n_entries, x.shape[1], x.dtype) and self.w_down.shape[2] % 8 == 0:
-            act = ops.moe_gemv(x, self.w_gate_up, None, chosen, per_token=True, gated=self.gated)
+            act = ops.moe_gemv(x, self.w_gate_up, None, chosen, per_token=True, gated=self.gated,
+                               act=self.act)
             y = ops.moe_gemv(act, self.w_down, None, chosen, per_token=False)
             return ops.moe_combine_weighted(y, None, chosen, weight, x, E)
         route = ops.moe_route(None, chosen, E, self.outputs)
@@ -173,9 +192,12 @@ class RoutedMoE:
             rows = ops.moe_gather_rows(x, route, E, top)
             gu = ops.library_grouped_product(rows, self.w_gate_up, route)
             if gu is not None:
-                y = ops.library_grouped_product(ops.clamped_gate_up(gu, *self.gated), self.w_down, route)
+                mid = (ops.clamped_gate_up(gu, *self.gated) if self.act is None
+                       else ops.unary_act(gu, self.act))
+                y = ops.library_grouped_product(mid, self.w_down, route)
                 if y is not None:
                     return ops.moe_combine_weighted(y, ops._route_parts(route, E)[2], chosen, weight, x, E)
-        act = ops.grouped_product(x, self.w_gate_up, route=route, top=top, gather=True, gated=self.gated)
+        act = ops.grouped_product(x, self.w_gate_up, route=route, top=top, gather=True, gated=self.gated,
+                                  act=self.act)
         y = ops.grouped_product(act, self.w_down, route=route, top=top, scatter=True, out_float32=True)
         return ops.moe_combine_weighted(y, None, chosen, weight, x, E)

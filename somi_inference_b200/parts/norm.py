@@ -10,7 +10,8 @@ from __future__ import annotations
 
 import torch
 
-from .base import BuildContext, GatedDelta, NormedDelta, ScaledBranches, TensorDecl, names_of
+from .base import (BranchSum, BuildContext, GatedDelta, NormedDelta, ScaledBranches, TensorDecl,
+                   names_of)
 from .registry import NORMS
 
 
@@ -33,6 +34,8 @@ class RMSNorm:
         `NormedDelta`: the branch's result passes an RMS norm of its own before it is added."""
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=residual.device)
+        if isinstance(delta, BranchSum):
+            delta = ScaledBranches(delta.a, None, delta.b, None, 1.0)
         if isinstance(delta, ScaledBranches):
             self.ctx.ops.add_scaled_rmsnorm(residual, delta.a, delta.scale_a, delta.b, delta.scale_b,
                                             delta.mult, delta.extra, self.weight, None, self.eps,
@@ -71,7 +74,8 @@ class RMSNorm:
 class LayerNorm:
     """(x - mean) / sqrt(var + eps) * weight, var the mean of the squared deviations; a weight and
     no bias.  Mean, variance and the residual sum are float32.  `delta` may be a `GatedDelta`:
-    the branch's result is then multiplied by sigmoid(gate logits) as it is added."""
+    the branch's result is then multiplied by sigmoid(gate logits) as it is added; or a
+    `BranchSum`: both results of the layer before are added."""
 
     @staticmethod
     def declare(params) -> list[TensorDecl]:
@@ -86,10 +90,15 @@ class LayerNorm:
 
     def forward(self, residual: torch.Tensor, delta=None,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
-        gate = None
+        gate = extra = None
         if isinstance(delta, GatedDelta):
             delta, gate = delta.delta, delta.gate_logits
+        elif isinstance(delta, BranchSum):
+            delta, extra = delta.a, delta.b
+            if extra is not None and extra.dtype != torch.float32:
+                extra = extra.float()
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=residual.device)
-        self.ctx.ops.add_layernorm(residual, delta, gate, self.weight, self.eps, out, rows)
+        self.ctx.ops.add_layernorm(residual, delta, gate, self.weight, self.eps, out, rows,
+                                   extra=extra)
         return out

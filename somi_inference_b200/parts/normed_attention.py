@@ -5,10 +5,14 @@ Per token, with h the mixer's input:
     q, k: every head divided by its root mean square over the head (eps inside the root) and
           multiplied by a weight of the head's width that all heads share     (`head_norm`)
     q, k: entry i < dims / 2 of a head is paired with entry i + dims / 2; the pair of the token at
-          position p turns by p * base^(-2i / dims); entries from `dims` on pass      (`rotary`)
-    scores q.k * scale over the keys the mask leaves: all earlier ones, or the token's own and
-          the `size` - 1 before it (`mask` = {"kind": "window", "size"}); softmax
-    out = Wo heads
+          position p turns by p * base^(-2i / dims); entries from `dims` on pass      (`rotary`;
+          its `scaling` changes the frequencies: `position.rotary_frequencies`)
+    scores q.k * scale, then cap * tanh(score / cap) where there is a `softcap`, over the keys the
+          mask leaves: all earlier ones, or the token's own and the `size` - 1 before it
+          (`mask` = {"kind": "window", "size"}); softmax, with `sink` = "zero" one more term
+          exp(0) in its denominator that has no value ("learned": exp of a stored score per head)
+    head i's output times sigmoid(Wg h)_i, one logit per head                      (`head_gate`)
+    out = Wo heads (+ bo: `o_bias`)
 Key and value widths may differ; query head i reads key/value head i // (heads / kv_heads).
 
 One product makes q, k and v; one kernel normalises, rotates and writes keys and values to their
@@ -22,6 +26,7 @@ import torch
 
 from .base import BuildContext, CacheNeeds, PagedKVNeeds, TensorDecl, names_of
 from .linear import Linear
+from .position import rotary_frequencies
 from .registry import MIXERS
 
 
@@ -47,7 +52,13 @@ class NormedAttentionMixer:
         if params.get("head_norm"):
             decl += [TensorDecl(n["q_norm"], (d,), init="ones", matrix=False),
                      TensorDecl(n["k_norm"], (d,), init="ones", matrix=False)]
+        if params.get("head_gate"):
+            decl.append(TensorDecl(n["gate_weight"], (heads, hidden)))
+        if params.get("sink") == "learned":
+            decl.append(TensorDecl(n["sink"], (heads,), init="zeros", matrix=False))
         decl.append(TensorDecl(n["o_weight"], (hidden, heads * dv)))
+        if params.get("o_bias"):
+            decl.append(TensorDecl(n["o_bias"], (hidden,), init="zeros", matrix=False))
         return decl
 
     def __init__(self, params, tensors, ctx: BuildContext) -> None:
@@ -70,21 +81,34 @@ class NormedAttentionMixer:
         self.rotary_dim = int(rotary.get("dims", 0))
         if self.rotary_dim % 2 or self.rotary_dim > self.key_dim:
             raise ValueError("rotary dims must be even and at most the key width")
-        if self.rotary_dim:
-            i = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64)
-            inv = float(rotary["base"]) ** (-i / self.rotary_dim)
-        else:
-            inv = torch.zeros(1, dtype=torch.float64)
+        inv, self.magnitude = rotary_frequencies(rotary)
         self.inv_freq = inv.to(ctx.device)
+        self.softcap = float(params["softcap"]) if params.get("softcap") else None
+        sink = params.get("sink")
+        if sink not in (None, "zero", "learned"):
+            raise ValueError(f"unknown sink {sink!r} (kinds: 'zero', 'learned')")
+        self.sinks = None
+        if sink == "zero":
+            self.sinks = torch.zeros(self.heads, dtype=torch.float32, device=ctx.device)
+        elif sink == "learned":
+            self.sinks = tensors[n["sink"]].float().contiguous()
         parts = ("q", "k", "v")
         bias = None
         if params.get("qkv_bias"):
             bias = torch.cat([tensors[n[p + "_bias"]].float() for p in parts], 0)
-        self.proj = Linear(torch.cat([tensors[n[p + "_weight"]] for p in parts], 0).contiguous(),
-                           bias, ctx.ops)
+        weights = [tensors[n[p + "_weight"]] for p in parts]
+        # the gate's logits are further columns of the same product
+        self.head_gate = bool(params.get("head_gate"))
+        self.gate_at = sum(w.shape[0] for w in weights)
+        if self.head_gate:
+            weights.append(tensors[n["gate_weight"]])
+            if bias is not None:
+                bias = torch.cat([bias, torch.zeros(self.heads, dtype=bias.dtype, device=bias.device)])
+        self.proj = Linear(torch.cat(weights, 0).contiguous(), bias, ctx.ops)
         self.q_norm = tensors[n["q_norm"]] if params.get("head_norm") else None
         self.k_norm = tensors[n["k_norm"]] if params.get("head_norm") else None
-        self.out = Linear(tensors[n["o_weight"]], None, ctx.ops)
+        self.out = Linear(tensors[n["o_weight"]],
+                          tensors[n["o_bias"]].float() if params.get("o_bias") else None, ctx.ops)
 
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds(paged=PagedKVNeeds(
@@ -98,10 +122,12 @@ class NormedAttentionMixer:
         ops.headnorm_rotary_store(qkv, batch.positions, self.inv_freq, self.heads, self.kv_heads,
                                   self.key_dim, self.value_dim, self.rotary_dim, self.q_norm,
                                   self.k_norm, self.eps, group.slot_map if owns_cache else None,
-                                  paged.keys, paged.values)
+                                  paged.keys, paged.values, magnitude=self.magnitude)
         out = torch.empty((x.shape[0], self.heads * self.value_dim), dtype=x.dtype, device=x.device)
         ops.paged_attention(qkv, paged.keys, paged.values, batch, group, self.heads, self.kv_heads,
                             self.key_dim, self.scale, self.window, out, storage=paged.storage,
-                            value_dim=self.value_dim)
+                            value_dim=self.value_dim,
+                            gate=qkv[:, self.gate_at:self.gate_at + self.heads] if self.head_gate else None,
+                            gate_per_head=self.head_gate, softcap=self.softcap, sinks=self.sinks)
         partial = self.out.partial_sums(out)
         return partial if partial is not None else self.out(out)

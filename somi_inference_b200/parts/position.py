@@ -77,3 +77,52 @@ class NoPositionEncoding:
             group.slot_map if (write and group is not None) else None,
             paged.keys if paged is not None else None,
             paged.values if paged is not None else None, partials=partials, bias=bias)
+
+
+def rotary_frequencies(rotary) -> tuple[torch.Tensor, float]:
+    """(float64 frequencies of the dims / 2 pairs, factor on every sine and cosine) of a rotation
+    {"dims", "base", "scaling": None | {...}}.  Pair i turns by position * base^(-2i / dims) where
+    nothing is scaled.  Scalings, by `kind`:
+
+    "bands" {factor, low, high, original}: with wavelength l = 2 pi / f, pairs with
+        l < original / high keep f, pairs with l > original / low get f / factor, and between
+        the two s = (original / l - low) / (high - low) blends (1 - s) f / factor + s f.
+    "ramp" {factor, original, fast, slow}: with index(t) = dims ln(original / (2 pi t)) /
+        (2 ln base), lo = max(floor(index(fast)), 0), hi = min(ceil(index(slow)), dims - 1) and
+        r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i gets f / factor * r_i +
+        f * (1 - r_i), and sines and cosines are multiplied by 0.1 ln(factor) + 1.
+    """
+    import math
+    dims = int(rotary.get("dims", 0)) if rotary else 0
+    if dims == 0:
+        return torch.zeros(1, dtype=torch.float64), 1.0
+    base = float(rotary["base"])
+    freq = [base ** (-2.0 * i / dims) for i in range(dims // 2)]
+    scaling = rotary.get("scaling")
+    if not scaling:
+        return torch.tensor(freq, dtype=torch.float64), 1.0
+    kind, factor, original = scaling["kind"], float(scaling["factor"]), float(scaling["original"])
+    if kind == "bands":
+        low, high = float(scaling["low"]), float(scaling["high"])
+        out = []
+        for f in freq:
+            wave = 2.0 * math.pi / f
+            if wave < original / high:
+                out.append(f)
+            elif wave > original / low:
+                out.append(f / factor)
+            else:
+                s = (original / wave - low) / (high - low)
+                out.append((1.0 - s) * f / factor + s * f)
+        return torch.tensor(out, dtype=torch.float64), 1.0
+    if kind == "ramp":
+        def index(turns: float) -> float:
+            return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+        lo = max(math.floor(index(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(index(float(scaling["slow"]))), dims - 1)
+        out = []
+        for i, f in enumerate(freq):
+            r = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f / factor * r + f * (1.0 - r))
+        return torch.tensor(out, dtype=torch.float64), 0.1 * math.log(factor) + 1.0
+    raise ValueError(f"unknown rotary scaling {kind!r} (kinds: 'bands', 'ramp')")

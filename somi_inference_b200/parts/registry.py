@@ -56,3 +56,4 @@ EMBEDDINGS = PartRegistry("embedding")
 HEADS = PartRegistry("head")
 ARRANGEMENTS = PartRegistry("block arrangement")
 LAYER_EXTRAS = PartRegistry("layer extra")
+STREAM_PARTS = PartRegistry("stream part")
