@@ -214,10 +214,24 @@ def choose_experts(logits, top):
     return order, e / e.sum(dim=-1, keepdim=True)
 
 
-def expert_mixture(h, w, p, mlp):
+def choice_margin(logits, top, least_weight=0.02):
+    """[S]: by how much the last chosen logit beats the best one left out, infinite where nothing
+    is left out or where the last chosen weighs less than `least_weight` (a swap changes little)."""
+    S, E = logits.shape
+    if top >= E:
+        return torch.full((S,), float("inf"), dtype=logits.dtype)
+    ordered = torch.sort(logits, dim=-1, descending=True).values
+    _, wt = choose_experts(logits, top)
+    gap = ordered[:, top - 1] - ordered[:, top]
+    return torch.where(wt[:, top - 1] < least_weight, torch.full_like(gap, float("inf")), gap)
+
+
+def expert_mixture(h, w, p, mlp, margins=None):
     """y_t = sum over the chosen experts of weight * W_down gelu(W_up h_t)."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     idx, wt = choose_experts(h @ w[p + "router"].T, top)
+    if margins is not None:
+        margins.append(choice_margin(h @ w[p + "router"].T, top))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(top):
@@ -250,9 +264,10 @@ def mixer(kind, h, w, p, m, eps):
     raise ValueError(kind)
 
 
-def forward(cfg, w, tokens, dtype=torch.float64, streams=None):
+def forward(cfg, w, tokens, dtype=torch.float64, streams=None, margins=None):
     """Logits [S, vocab] of one sequence.  `streams`: a list that receives the residual stream
-    after every layer run."""
+    after every layer run; `margins`: one that receives a tensor [S] per mixture of experts that
+    ran (see `choice_margin`)."""
     w = {n: t.to(dtype) if t.is_floating_point() else t for n, t in w.items()}
     eps = cfg["norm"]["eps"]
     x0 = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
@@ -264,8 +279,16 @@ def forward(cfg, w, tokens, dtype=torch.float64, streams=None):
         h = layer_norm(x, w[f"l{i}.norm1"], eps)
         y = mixer(layer["type"], h, w, f"l{i}.mix.", layer["mixer"], eps)
         if layer.get("mlp") is not None:
-            y = y + expert_mixture(h, w, f"l{i}.mlp.", layer["mlp"])
+            y = y + expert_mixture(h, w, f"l{i}.mlp.", layer["mlp"], margins)
         x = x + y
         if streams is not None:
             streams.append(x.clone())
     return layer_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def greedy(cfg, weights, prompt, n_new, dtype=torch.float64):
+    """Greedy continuation by recomputing the whole sequence for every new token."""
+    seq = list(prompt)
+    for _ in range(n_new):
+        seq.append(int(forward(cfg, weights, seq, dtype)[-1].argmax()))
+    return seq[len(prompt):]
