@@ -7,6 +7,7 @@
     python bench.py --arch digosun --only decode|prefill [...]   the same shapes with Digosun layers
     python bench.py --arch dapozen --only decode|prefill [...]   the same shapes with Dapozen layers
     python bench.py --arch poselorn --only decode|prefill [...]  the same shapes with Poselorn layers
+    python bench.py --arch gikarax --only decode|prefill [...]   the same shapes with Gikarax layers
 
 A step is one decode step of the whole engine: 8 requests with 2,048 cached tokens each,
 random bfloat16 weights, one new token per request (batch layout upload, all layers, head,
@@ -74,6 +75,14 @@ DAPOZEN = dict(chunk=8192, taps=4, ssm_head=64, ssm_state=128, ssm_groups=4, exp
 # widths; sixteen experts of a quarter of the dense feed-forward's width and four identity experts
 # in four groups of which three are kept, three per token.
 POSELORN = dict(window=8192, taps=4, rank=128, experts=16, identity=4, top=3, groups=(4, 3))
+# `--arch gikarax`: the same widths, head counts, head sizes and vocabularies with Gikarax layers in
+# the pattern latent attention, window attention (capped scores, a sink, gates per head), window
+# attention, causal attention beside a gated linear attention; every layer with sixteen experts
+# of a quarter of the dense feed-forward's width, four per token; the last three layers of every
+# four are a loop that runs twice, so the stream is re-mixed with the embedding twice.  The
+# latents are Digosun's; the window is longer than the timed contexts (the attention reads what
+# the Qwen2 layer reads); the linear attention has the shape's heads at the same widths.
+GIKARAX = dict(window=8192, softcap=50.0, rank=128, tau=16.0, experts=16, top=4)
 CONTEXT = 2048          # cached tokens per request when decode is timed
 MAX_CONTEXT = 4096      # "benchmark at context 4096": positions the model is laid out for
 LONG_CONTEXT = 40960    # ... when the points at 8 k and 32 k cached tokens are measured too
@@ -269,13 +278,39 @@ def poselorn_config(shape: str, layers: int, positions: int) -> dict:
             "layers": [dict(zip(("type", "mixer", "mlp"), pattern[i % 4])) for i in range(layers)]}
 
 
+def gikarax_config(shape: str, layers: int, positions: int) -> dict:
+    q, z, lat = SHAPES[shape], GIKARAX, DIGOSUN_SHAPES[shape]
+    D, hd, H, G = q["hidden_size"], q["head_dim"], q["num_attention_heads"], q["num_key_value_heads"]
+    latent = dict(heads=H, dim=hd, vdim=hd, q_rank=lat["q_rank"], kv_rank=lat["kv_rank"], scale=hd ** -0.5)
+    window = dict(heads=H, kv_heads=G, dim=hd, vdim=hd, scale=hd ** -0.5, softcap=z["softcap"],
+                  mask={"size": z["window"]},
+                  rot={"dims": hd // 2, "base": q["rope_theta"],
+                       "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
+    left = dict(heads=H, kv_heads=G, dim=hd, vdim=hd, scale=hd ** -0.5,
+                rot={"dims": hd // 2, "base": q["rope_theta"],
+                     "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}})
+    right = dict(heads=H, dim=hd, vdim=hd, tau=z["tau"], decay_rank=z["rank"])
+    moe = {"kind": "moe", "expert": {"ff": q["intermediate_size"] // 4},
+           "router": {"experts": z["experts"], "top": z["top"]}}
+    pattern = [("latent_attention", latent), ("attention", window), ("attention", window),
+               ("parallel", {"left": left, "right": right})]
+    cfg = {"architecture": "Gikarax", "vocab": q["vocab_size"], "width": D,
+           "norm": {"eps": q["rms_norm_eps"]}, "max_positions": positions,
+           "layers": [{"type": pattern[i % 4][0], "mixer": pattern[i % 4][1], "mlp": moe}
+                      for i in range(layers)]}
+    if layers >= 2:
+        cfg["loop"] = {"start": 1, "stop": min(layers, 4), "times": 2}
+    return cfg
+
+
 ARCH = "qwen2"     # set by --arch; the other architectures build the same shapes with their layers
 
 
 def build_engine(shape: str, layers: int, max_tokens: int, max_requests: int, positions: int):
     import torch
 
-    from somi_inference_b200.config import DapozenConfig, DigosunConfig, PoselornConfig, Qwen2Config
+    from somi_inference_b200.config import (DapozenConfig, DigosunConfig, GikaraxConfig,
+                                            PoselornConfig, Qwen2Config)
     from somi_inference_b200.engine import Engine
     from somi_inference_b200.parts import declared_tensors
     if ARCH == "digosun":
@@ -284,6 +319,8 @@ def build_engine(shape: str, layers: int, max_tokens: int, max_requests: int, po
         cfg = DapozenConfig.from_dict(dapozen_config(shape, layers, positions))
     elif ARCH == "poselorn":
         cfg = PoselornConfig.from_dict(poselorn_config(shape, layers, positions))
+    elif ARCH == "gikarax":
+        cfg = GikaraxConfig.from_dict(gikarax_config(shape, layers, positions))
     else:
         cfg = Qwen2Config.from_dict(shape_config(shape, layers, positions))
     gen = torch.Generator(device="cuda").manual_seed(0)
@@ -427,7 +464,65 @@ def poselorn_sizes(cfg, batch: int) -> dict:
             "state_bytes_per_request": state, "window": min(windows)}
 
 
+def gikarax_sizes(cfg, batch: int) -> dict:
+    """The same figures for a Gikarax model, run by run (a looped layer counts every time).  A
+    decode step of `batch` tokens reads at most batch * top experts of a layer; the latent cache
+    holds kv_rank numbers a position, read once for all heads; every matrix state is read and
+    written once per request and step in float32 (5 flops per state entry and token)."""
+    D, V = cfg.width, cfg.vocab
+    params = read_params = small = kv = pair = state = 0
+    windows = []
+    for i, opens in cfg.runs():
+        layer = cfg.layers[i]
+        m = layer.mixer
+        if opens:
+            params += 2 * D * D
+            read_params += 2 * D * D
+        if layer.type == "latent_attention":
+            inner = m["heads"] * m["vdim"]
+            p = (m["q_rank"] + m["kv_rank"] + inner) * D + m["heads"] * m["dim"] * m["q_rank"] \
+                + m["heads"] * (m["dim"] + m["vdim"]) * m["kv_rank"] + D * inner
+            small += m["q_rank"] + m["kv_rank"]
+            kv += 2 * m["kv_rank"]
+            pair += 4 * m["heads"] * m["kv_rank"]
+            windows.append(1 << 30)
+        elif layer.type == "attention":
+            qkv = (m["heads"] + m["kv_heads"]) * m["dim"] + m["kv_heads"] * m["vdim"] + m["heads"]
+            p = qkv * D + D * m["heads"] * m["vdim"]
+            small += 2 * m["dim"]
+            kv += 2 * m["kv_heads"] * (m["dim"] + m["vdim"])
+            pair += 2 * m["heads"] * (m["dim"] + m["vdim"])
+            windows.append(m["mask"]["size"] if m.get("mask") else 1 << 30)
+        else:
+            a, b = m["left"], m["right"]
+            qkv = (a["heads"] + a["kv_heads"]) * a["dim"] + a["kv_heads"] * a["vdim"]
+            r = b.get("decay_rank", 16)
+            p = qkv * D + D * a["heads"] * a["vdim"]
+            p += (2 * b["heads"] * b["dim"] + 2 * b["heads"] * b["vdim"] + r) * D + b["heads"] * b["dim"] * r \
+                + D * b["heads"] * b["vdim"]
+            p += 5 * b["heads"] * b["dim"] * b["vdim"] // 2
+            small += qkv + D + b["heads"] * b["dim"] + b["vdim"] + 2 * D
+            kv += 2 * a["kv_heads"] * (a["dim"] + a["vdim"])
+            pair += 2 * a["heads"] * (a["dim"] + a["vdim"])
+            state += 2 * 4 * b["heads"] * b["dim"] * b["vdim"]
+            windows.append(1 << 30)
+        params += p
+        read_params += p
+        small += D
+        mlp = layer.mlp
+        if mlp is not None:
+            r = mlp["router"]
+            one = 2 * D * mlp["expert"]["ff"]
+            params += r["top"] * one + r["experts"] * D
+            read_params += min(r["experts"], batch * r["top"]) * one + r["experts"] * D
+    return {"weight_bytes": 2 * (read_params + small + V * D + D), "kv_bytes_per_token": kv,
+            "matmul_params": params, "head_params": V * D, "attn_flops_per_pair": pair,
+            "state_bytes_per_request": state, "window": min(windows)}
+
+
 def model_sizes(cfg, layers: int, batch: int = 1) -> dict:
+    if ARCH == "gikarax":
+        return gikarax_sizes(cfg, batch)
     if ARCH == "digosun":
         return digosun_sizes(cfg)
     if ARCH == "poselorn":
@@ -1025,10 +1120,12 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--shape", choices=list(SHAPES), default="7b")
-    ap.add_argument("--arch", choices=["qwen2", "digosun", "dapozen", "poselorn"], default="qwen2",
+    ap.add_argument("--arch", choices=["qwen2", "digosun", "dapozen", "poselorn", "gikarax"], default="qwen2",
                     help="with --only decode|prefill: the layer design the shape is built with "
                          "(digosun: latent attention under a window, gated branches; dapozen: "
-                         "chunked attention with convolutions, Mamba-2 layers, table-routed experts)")
+                         "chunked attention with convolutions, Mamba-2 layers, table-routed experts; "
+                         "gikarax: latent, capped window and causal attention, a gated linear "
+                         "attention, experts without gates, a loop)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true",

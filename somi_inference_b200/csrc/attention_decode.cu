@@ -42,7 +42,8 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
                           const __nv_bfloat16* __restrict__ vcache,
                           const int* __restrict__ block_table, int bt_stride,
                           const int* __restrict__ ctx_len, int nq, int nkv, int page_size,
-                          float scale_log2e, int window, float* __restrict__ part_o,
+                          float scale_log2e, int window, float cap_in, float cap_out,
+                          const float* __restrict__ sinks, float* __restrict__ part_o,
                           float* __restrict__ part_ml, int max_splits,
                           __nv_bfloat16* __restrict__ out) {
     constexpr int CPR = HD / 8;
@@ -127,7 +128,7 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
         for (int e = 0; e < 4; ++e) {
             const int key = k0 + kw + nt * 8 + (lane & 3) * 2 + (e & 1);
             const bool ok = key < rg.kv_len && key >= rg.first_key;
-            const float v = ok ? s[nt][e] * scale_log2e : -INFINITY;
+            const float v = ok ? score_log2(s[nt][e], scale_log2e, cap_in, cap_out) : -INFINITY;
             s[nt][e] = v;
             if (e < 2) m_lo = fmaxf(m_lo, v); else m_hi = fmaxf(m_hi, v);
         }
@@ -209,6 +210,7 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
         }
         const int head = kvh * G + g;
         if (single) {
+            if (sinks != nullptr) L += exp2f(sinks[head] * 1.4426950408889634f - M);
             out[static_cast<size_t>(row) * nq * HD + head * HD + d] = __float2bfloat16_rn(acc / L);
         } else {
             const size_t p = (static_cast<size_t>(i) * nq + head) * max_splits + split;
@@ -222,7 +224,8 @@ template <int HD>
 int launch_decode(const void* qkv, int row_stride, int row_base, int req_base, int n_decode,
                   const void* kcache, const void* vcache, const int* block_table, int bt_stride,
                   const int* ctx_len, int nq, int nkv, int page_size, float scale, int window,
-                  float* part_o, float* part_ml, int max_splits, void* out, cudaStream_t stream) {
+                  float* part_o, float* part_ml, int max_splits, void* out, cudaStream_t stream,
+                  float softcap, const float* sinks) {
     const size_t smem = static_cast<size_t>(kDecRows + 2 * kDecChunk) * HD * 2;
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(paged_decode_split_kernel<HD>,
@@ -232,11 +235,14 @@ int launch_decode(const void* qkv, int row_stride, int row_base, int req_base, i
         static_cast<const __nv_bfloat16*>(qkv), row_stride, row_base, req_base,
         static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache),
         block_table, bt_stride, ctx_len, nq, nkv, page_size, scale * 1.4426950408889634f, window,
+        softcap > 0.f ? 2.0f * 1.4426950408889634f * scale / softcap : 0.f,
+        softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, sinks,
         part_o, part_ml, max_splits, static_cast<__nv_bfloat16*>(out));
     int rc = launch_status();
     if (rc != 0 || max_splits == 1) return rc;
     return launch_decode_merge<HD>(part_o, part_ml, max_splits, kDecChunk, ctx_len, row_base, req_base,
-                                   n_decode, nq, window, static_cast<__nv_bfloat16*>(out), stream);
+                                   n_decode, nq, window, static_cast<__nv_bfloat16*>(out), stream,
+                                   sinks);
 }
 
 }  // namespace somi
@@ -253,11 +259,13 @@ SOMI_API int somi_decode_supported(int nq, int nkv, int hd) {
 }
 
 // Scratch: part_o float32 [n_decode, nq, max_splits, hd], part_ml float32 [n_decode, nq, max_splits, 2].
-SOMI_API int somi_paged_attention_decode(
+// `softcap` > 0: scores pass softcap * tanh(score / softcap); `sinks`: float32 [nq] scores that
+// join every softmax's denominator, or null.
+SOMI_API int somi_paged_attention_decode_shaped(
     const void* qkv, int row_stride, int row_base, int req_base, int n_decode, const void* kcache,
     const void* vcache, const int* block_table, int bt_stride, const int* ctx_len, int nq, int nkv,
-    int hd, int page_size, float scale, int window, float* part_o, float* part_ml, int max_splits,
-    void* out, cudaStream_t stream) {
+    int hd, int page_size, float scale, int window, float softcap, const float* sinks,
+    float* part_o, float* part_ml, int max_splits, void* out, cudaStream_t stream) {
     if (n_decode <= 0) return 0;
     if (!somi_decode_supported(nq, nkv, hd) || page_size <= 0 || max_splits <= 0 ||
         n_decode > 65535 || nkv > 65535)
@@ -265,11 +273,22 @@ SOMI_API int somi_paged_attention_decode(
 #define SOMI_DEC(HD)                                                                             \
     return launch_decode<HD>(qkv, row_stride, row_base, req_base, n_decode, kcache, vcache,      \
                              block_table, bt_stride, ctx_len, nq, nkv, page_size, scale, window, \
-                             part_o, part_ml, max_splits, out, stream)
+                             part_o, part_ml, max_splits, out, stream, softcap, sinks)
     if (hd == 32) SOMI_DEC(32);
     if (hd == 64) SOMI_DEC(64);
     SOMI_DEC(128);
 #undef SOMI_DEC
+}
+
+SOMI_API int somi_paged_attention_decode(
+    const void* qkv, int row_stride, int row_base, int req_base, int n_decode, const void* kcache,
+    const void* vcache, const int* block_table, int bt_stride, const int* ctx_len, int nq, int nkv,
+    int hd, int page_size, float scale, int window, float* part_o, float* part_ml, int max_splits,
+    void* out, cudaStream_t stream) {
+    return somi_paged_attention_decode_shaped(qkv, row_stride, row_base, req_base, n_decode, kcache,
+                                              vcache, block_table, bt_stride, ctx_len, nq, nkv, hd,
+                                              page_size, scale, window, 0.f, nullptr, part_o,
+                                              part_ml, max_splits, out, stream);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -170,9 +170,41 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int row_stride,
     }
 }
 
+// x[t, h * vd + d] *= sigmoid(gate[t * gate_stride + h]): one logit per token and head, for the
+// attention kernels that leave the gate to a kernel of its own.
+template <typename T>
+__global__ void head_gate_mul_kernel(T* __restrict__ x, const T* __restrict__ gate, long long gate_stride,
+                                     int heads, int vd, long long n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long per_row = static_cast<long long>(heads) * vd;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long t = i / per_row;
+        const int h = static_cast<int>((i - t * per_row) / vd);
+        const float z = to_float(gate[t * gate_stride + h]);
+        x[i] = from_float<T>(to_float(x[i]) / (1.0f + expf(-z)));
+    }
+}
+
 }  // namespace somi
 
 using namespace somi;
+
+SOMI_API int somi_head_gate_mul(void* x, const void* gate, int dtype, long long gate_stride,
+                                long long rows, int heads, int vd, cudaStream_t stream) {
+    const long long n = rows * heads * vd;
+    if (n <= 0) return 0;
+    const int blocks = static_cast<int>(((n + 255) / 256) < 148LL * 16 ? ((n + 255) / 256) : 148LL * 16);
+    if (dtype == SOMI_F32)
+        launch_pdl(head_gate_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream,
+                   static_cast<float*>(x), static_cast<const float*>(gate), gate_stride, heads, vd, n);
+    else
+        launch_pdl(head_gate_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                   static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gate),
+                   gate_stride, heads, vd, n);
+    return launch_status();
+}
 
 SOMI_API int somi_attention_generic_q_tile() { return kBM; }
 

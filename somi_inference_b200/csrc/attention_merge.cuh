@@ -1,5 +1,6 @@
 // Merge of the partial results of split-KV decode attention: for every (request, query head)
 // the chunks' outputs, each with its maximum and sum, are added up into one bfloat16 row.
+// `sinks` (float32 per query head, or null): a score that joins the denominator without a value.
 //
 // Two kernels.  Few chunks: one thread per output element walks through them (the chain is
 // short and the launch is what counts).  Many chunks (long contexts): the warps of the CTA
@@ -35,7 +36,8 @@ template <int HD, int CHUNK>
 __global__ void __launch_bounds__(HD)
 decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                     int max_splits, const int* __restrict__ ctx_len, int row_base,
-                    int req_base, int nq, int window, __nv_bfloat16* __restrict__ out) {
+                    int req_base, int nq, int window, const float* __restrict__ sinks,
+                    __nv_bfloat16* __restrict__ out) {
     const int i = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
     pdl_launch_dependents();
     pdl_wait();
@@ -50,6 +52,7 @@ decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ 
         acc += f * part_o[(base + s) * HD + d];
         L += f * part_ml[2 * (base + s) + 1];
     }
+    if (sinks != nullptr) L += exp2f(sinks[head] * 1.4426950408889634f - M);
     out[static_cast<size_t>(row_base + i) * nq * HD + head * HD + d] = __float2bfloat16_rn(acc / L);
 }
 
@@ -57,7 +60,8 @@ template <int HD>
 __global__ void __launch_bounds__(kMergeWarps * 32)
 decode_merge_wide_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                          int max_splits, int chunk, const int* __restrict__ ctx_len, int row_base,
-                         int req_base, int nq, int window, __nv_bfloat16* __restrict__ out) {
+                         int req_base, int nq, int window, const float* __restrict__ sinks,
+                         __nv_bfloat16* __restrict__ out) {
     constexpr int V = (HD + 31) / 32;                     // output elements per lane
     __shared__ float red_o[kMergeWarps][HD];
     __shared__ float red_l[kMergeWarps];
@@ -106,6 +110,7 @@ decode_merge_wide_kernel(const float* __restrict__ part_o, const float* __restri
             a += red_o[w][d];
             l += red_l[w];
         }
+        if (sinks != nullptr) l += exp2f(sinks[head] * 1.4426950408889634f - M);
         out[static_cast<size_t>(row_base + i) * nq * HD + head * HD + d] = __float2bfloat16_rn(a / l);
     }
 }
@@ -116,14 +121,15 @@ decode_merge_wide_kernel(const float* __restrict__ part_o, const float* __restri
 template <int HD>
 static int launch_decode_merge(const float* part_o, const float* part_ml, int max_splits, int chunk,
                         const int* ctx_len, int row_base, int req_base, int n_decode, int nq,
-                        int window, __nv_bfloat16* out, cudaStream_t stream) {
+                        int window, __nv_bfloat16* out, cudaStream_t stream,
+                        const float* sinks = nullptr) {
     dim3 grid(n_decode, nq);
     if (max_splits >= kMergeWideFrom || chunk != 128)
         launch_pdl(decode_merge_wide_kernel<HD>, grid, dim3(kMergeWarps * 32), 0, stream, part_o,
-                   part_ml, max_splits, chunk, ctx_len, row_base, req_base, nq, window, out);
+                   part_ml, max_splits, chunk, ctx_len, row_base, req_base, nq, window, sinks, out);
     else
         launch_pdl(decode_merge_kernel<HD, 128>, grid, dim3(HD), 0, stream, part_o, part_ml,
-                   max_splits, ctx_len, row_base, req_base, nq, window, out);
+                   max_splits, ctx_len, row_base, req_base, nq, window, sinks, out);
     return launch_status();
 }
 

@@ -32,7 +32,8 @@ paged_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
                          long long v_row0, const int* __restrict__ block_table, int bt_stride,
                          const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                          const int* __restrict__ tiles, int nq, int nkv, int page_size,
-                         float scale_log2e, int window, __nv_bfloat16* __restrict__ out) {
+                         float scale_log2e, int window, float cap_in, float cap_out,
+                         const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out) {
     constexpr int CPR = HD / 8;
     constexpr int HALVES = HD / 64;
     constexpr int TILE = HALVES * kTpHalfBytes;                 // bytes of one K or V tile
@@ -157,7 +158,7 @@ paged_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
                         const int key = kb + nt * 8 + (lane & 3) * 2 + (e & 1);
                         const int pos = e < 2 ? pos_lo : pos_hi;
                         const bool ok = key <= pos && key >= kv_first && key >= first_visible_key(pos, window);
-                        const float v = ok ? s[nt][e] * scale_log2e : -INFINITY;
+                        const float v = ok ? score_log2(s[nt][e], scale_log2e, cap_in, cap_out) : -INFINITY;
                         s[nt][e] = v;
                         if (e < 2) t_lo = fmaxf(t_lo, v); else t_hi = fmaxf(t_hi, v);
                     }
@@ -166,7 +167,7 @@ paged_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
                 for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float v = s[nt][e] * scale_log2e;
+                        const float v = score_log2(s[nt][e], scale_log2e, cap_in, cap_out);
                         s[nt][e] = v;
                         if (e < 2) t_lo = fmaxf(t_lo, v); else t_hi = fmaxf(t_hi, v);
                     }
@@ -221,6 +222,11 @@ paged_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
 
     if (!copies_ok && lane == 0) atomicExch(&g_prefill_tma_error, 1);
     const int r_lo = qr + (lane >> 2), r_hi = r_lo + 8;
+    if (sinks != nullptr) {      // a score without a key or a value in every row's denominator
+        const float sk = sinks[head] * 1.4426950408889634f;
+        l_lo += m_lo == -INFINITY ? 0.f : exp2f(sk - m_lo);
+        l_hi += m_hi == -INFINITY ? 0.f : exp2f(sk - m_hi);
+    }
     const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt) {
@@ -239,7 +245,8 @@ template <int HD>
 int launch_prefill_tma(const CUtensorMap* map, const void* qkv, int row_stride, long long k_row0,
                        long long v_row0, const int* block_table, int bt_stride, const int* cu_q,
                        const int* ctx_len, const int* tiles, int n_tiles, int nq, int nkv,
-                       int page_size, float scale, int window, void* out, cudaStream_t stream) {
+                       int page_size, float scale, int window, float softcap, const float* sinks,
+                       void* out, cudaStream_t stream) {
     constexpr int TILE = (HD / 64) * kTpHalfBytes;
     const size_t smem = 4 * TILE + kTpBM * HD * 2 + 1024;
     cudaFuncSetAttribute(paged_prefill_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -248,7 +255,10 @@ int launch_prefill_tma(const CUtensorMap* map, const void* qkv, int row_stride, 
     launch_pdl(paged_prefill_tma_kernel<HD>, grid, dim3(kTpThreads), smem, stream, *map,
                static_cast<const __nv_bfloat16*>(qkv), row_stride, k_row0, v_row0, block_table,
                bt_stride, cu_q, ctx_len, tiles, nq, nkv, page_size,
-               scale * 1.4426950408889634f, window, static_cast<__nv_bfloat16*>(out));
+               scale * 1.4426950408889634f, window,
+               softcap > 0.f ? 2.0f * 1.4426950408889634f * scale / softcap : 0.f,
+               softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, sinks,
+               static_cast<__nv_bfloat16*>(out));
     return launch_status();
 }
 
@@ -270,19 +280,32 @@ SOMI_API int somi_prefill_tma_error() {
 }
 
 // `tensor_map`: the cache storage's map as made by somi_make_kv_tensor_map (boxes of one page).
-SOMI_API int somi_paged_attention_prefill_tma(
+// `softcap` > 0: scores pass softcap * tanh(score / softcap); `sinks`: float32 [nq] scores that
+// join every softmax's denominator, or null.
+SOMI_API int somi_paged_attention_prefill_tma_shaped(
     const void* tensor_map, const void* qkv, int row_stride, long long k_row0, long long v_row0,
     const int* block_table, int bt_stride, const int* cu_q, const int* ctx_len, const int* tiles,
-    int n_tiles, int nq, int nkv, int hd, int page_size, float scale, int window, void* out,
-    cudaStream_t stream) {
+    int n_tiles, int nq, int nkv, int hd, int page_size, float scale, int window, float softcap,
+    const float* sinks, void* out, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!somi_prefill_tma_supported(nq, nkv, hd, page_size) || nq > 65535) return SOMI_ERR_UNSUPPORTED;
     const CUtensorMap* map = static_cast<const CUtensorMap*>(tensor_map);
     if (hd == 64)
         return launch_prefill_tma<64>(map, qkv, row_stride, k_row0, v_row0, block_table, bt_stride,
                                       cu_q, ctx_len, tiles, n_tiles, nq, nkv, page_size, scale,
-                                      window, out, stream);
+                                      window, softcap, sinks, out, stream);
     return launch_prefill_tma<128>(map, qkv, row_stride, k_row0, v_row0, block_table, bt_stride,
                                    cu_q, ctx_len, tiles, n_tiles, nq, nkv, page_size, scale, window,
-                                   out, stream);
+                                   softcap, sinks, out, stream);
+}
+
+SOMI_API int somi_paged_attention_prefill_tma(
+    const void* tensor_map, const void* qkv, int row_stride, long long k_row0, long long v_row0,
+    const int* block_table, int bt_stride, const int* cu_q, const int* ctx_len, const int* tiles,
+    int n_tiles, int nq, int nkv, int hd, int page_size, float scale, int window, void* out,
+    cudaStream_t stream) {
+    return somi_paged_attention_prefill_tma_shaped(tensor_map, qkv, row_stride, k_row0, v_row0,
+                                                   block_table, bt_stride, cu_q, ctx_len, tiles,
+                                                   n_tiles, nq, nkv, hd, page_size, scale, window,
+                                                   0.f, nullptr, out, stream);
 }

@@ -60,6 +60,15 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// A score in base-2 units: s * scale * log2(e), or with a cap (cap_out != 0) the capped score
+// cap * tanh(s * scale / cap) * log2(e), where cap_in = 2 log2(e) scale / cap, cap_out = cap log2(e)
+// and tanh(y) = 1 - 2 / (1 + e^(2y)) (absolute error of the hardware 2^x and division: 1e-6 of the cap).
+__device__ __forceinline__ float score_log2(float s, float scale_log2e, float cap_in, float cap_out) {
+    if (cap_out == 0.f) return s * scale_log2e;
+    const float e = fast_exp2(fminf(s * cap_in, 80.f));
+    return cap_out * (1.0f - __fdividef(2.0f, 1.0f + e));
+}
+
 // Two float32 operations in one instruction (sm_100: `*.f32x2` on register pairs), and the maximum
 // of three.  They halve the instructions of loops that are bound by issue slots.
 __device__ __forceinline__ uint64_t pair_f32(float lo, float hi) {

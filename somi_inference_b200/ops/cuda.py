@@ -302,7 +302,10 @@ class CudaOps:
         value width] (rows may lie further apart); the output is multiplied by their sigmoid;
         with `gate_per_head` the logits are [T, nq], one per token and head.  `softcap`: scores
         pass cap * tanh(score / cap); `sinks`: float32 [nq] scores that join the softmax's
-        denominator without a key.  Capped scores, sinks and per-head gates run the generic kernel.
+        denominator without a key.  With capped scores or sinks, bfloat16 prompt portions of head
+        sizes 64/128 run the `mma.sync` kernel that TMA feeds and single tokens the cp.async
+        split-KV kernel (the tcgen05 kernels compute neither); a per-head gate is then a kernel
+        of its own behind them.
         """
         _check(qkv, kcache, vcache, out, group.block_table)
         assert kcache.dtype == qkv.dtype
@@ -320,13 +323,18 @@ class CudaOps:
             _check(sinks)
             assert sinks.dtype == torch.float32 and sinks.numel() == nq
         n_decode = batch.num_requests - batch.num_prefill_requests
-        # what the tensor-core kernels compute
-        plain = vd == hd and cap == 0.0 and sinks is None and not (gate is not None and gate_per_head)
+        # what the tensor-core kernels compute; they fetch query rows in 16-byte pieces
+        plain = vd == hd and qkv.shape[1] % 8 == 0
+        shaped = cap != 0.0 or sinks is not None
         if chunk and win:
             raise KernelError("a mask is a window or a chunk, not both")
         split = plain and n_decode > 0 and self.decode_supported(nq, nkv, hd, qkv.dtype)
         tensor_core_prefill = (plain and batch.num_prefill_requests > 0
                                and self.prefill_supported(nq, nkv, hd, qkv.dtype))
+        if shaped and tensor_core_prefill:      # only the TMA-fed mma.sync kernel shapes scores
+            tensor_core_prefill = (self.use_tma_prefill and storage is not None and bool(
+                self.lib.somi_prefill_tma_supported(ctypes.c_int(nq), ctypes.c_int(nkv),
+                                                    ctypes.c_int(hd), ctypes.c_int(page_size))))
         # the tensor-core kernels take the mask as one number: n > 0 a window, n < 0 a chunk of -n
         if chunk:
             win = -chunk
@@ -340,7 +348,20 @@ class CudaOps:
             row_bytes = hd * 2
             # (the two-tile kernel has half as many CTAs: below one per SM the one-tile kernel,
             # with twice as many, is the faster: 0.5B shape at 2,048 tokens 123 vs 148 TFLOP/s)
-            if (self.use_pp_prefill and storage is not None and qkv.shape[1] % 8 == 0
+            if shaped:
+                tiles = batch.tiles[self.prefill_q_tile]
+                rc = self.lib.somi_paged_attention_prefill_tma_shaped(
+                    ctypes.c_void_p(self._kv_tensor_map(storage, hd, page_size)), _ptr(qkv),
+                    ctypes.c_int(qkv.shape[1]),
+                    ctypes.c_longlong((kcache.data_ptr() - storage.data_ptr()) // row_bytes),
+                    ctypes.c_longlong((vcache.data_ptr() - storage.data_ptr()) // row_bytes),
+                    _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
+                    _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]), *sizes,
+                    ctypes.c_float(scale), ctypes.c_int(win), ctypes.c_float(cap), _ptr(sinks),
+                    _ptr(out), self._stream())
+                self._done(rc, "paged_attention_prefill_tma")
+                kernel = "attention_prefill_tma"
+            elif (self.use_pp_prefill and storage is not None and qkv.shape[1] % 8 == 0
                     and batch.tiles[self.prefill_pp_q_tile].shape[0] * nq >= self.pp_prefill_min_ctas
                     and bool(self.lib.somi_prefill_pp_supported(*sizes))):
                 tiles = batch.tiles[self.prefill_pp_q_tile]
@@ -418,7 +439,7 @@ class CudaOps:
             max_splits = -(-group.width * page_size // chunk)
             n_o = n_decode * nq * max_splits * hd
             ws = self._scratch(n_o + n_decode * nq * max_splits * 2, qkv.device)
-            tma = (self.use_tma_decode and storage is not None and bool(
+            tma = (not shaped and self.use_tma_decode and storage is not None and bool(
                 self.lib.somi_decode_tma_supported(ctypes.c_int(nq), ctypes.c_int(nkv),
                                                    ctypes.c_int(hd), ctypes.c_int(page_size))))
             if tma:
@@ -436,13 +457,14 @@ class CudaOps:
                     ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(ws.data_ptr() + 4 * n_o),
                     ctypes.c_int(max_splits), _ptr(out), self._stream())
             else:
-                rc = self.lib.somi_paged_attention_decode(
+                rc = self.lib.somi_paged_attention_decode_shaped(
                     _ptr(qkv), ctypes.c_int(qkv.shape[1]), ctypes.c_int(batch.num_prefill_tokens),
                     ctypes.c_int(batch.num_prefill_requests), ctypes.c_int(n_decode),
                     _ptr(kcache), _ptr(vcache), _ptr(group.block_table),
                     ctypes.c_int(group.width), _ptr(batch.ctx_len), ctypes.c_int(nq),
                     ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size),
-                    ctypes.c_float(scale), ctypes.c_int(win), ctypes.c_void_p(ws.data_ptr()),
+                    ctypes.c_float(scale), ctypes.c_int(win), ctypes.c_float(cap), _ptr(sinks),
+                    ctypes.c_void_p(ws.data_ptr()),
                     ctypes.c_void_p(ws.data_ptr() + 4 * n_o), ctypes.c_int(max_splits),
                     _ptr(out), self._stream())
             self._done(rc, "paged_attention_decode")
@@ -459,7 +481,16 @@ class CudaOps:
             # the generic kernel applied the gate to its own rows only
             first = 0 if tensor_core_prefill else batch.num_prefill_tokens
             last = batch.num_tokens if split else batch.num_prefill_tokens
-            self.sigmoid_gate_mul(out[first:last], gate[first:last])
+            if gate_per_head:
+                rc = self.lib.somi_head_gate_mul(
+                    _ptr(out[first:last]), _ptr(gate[first:last]), _code(out),
+                    ctypes.c_longlong(gate.stride(0)), ctypes.c_longlong(last - first),
+                    ctypes.c_int(nq), ctypes.c_int(vd), self._stream())
+                self._done(rc, "head_gate_mul")
+                if trace.active():
+                    trace.note("head_gate_mul", 2 * (last - first) * nq * vd * out.element_size())
+            else:
+                self.sigmoid_gate_mul(out[first:last], gate[first:last])
 
     # ------------------------------------------------ gated layers, latent attention
     def embed_sinusoid_layernorm(self, ids, positions, table, inv_freq, weight, eps, out) -> None:

@@ -101,9 +101,13 @@ class NormedAttentionMixer:
         self.head_gate = bool(params.get("head_gate"))
         self.gate_at = sum(w.shape[0] for w in weights)
         if self.head_gate:
-            weights.append(tensors[n["gate_weight"]])
+            # (rows of zeros behind them keep the product's rows a multiple of 16 bytes, which the
+            # tensor-core attention kernels need to fetch the queries)
+            gate_w = tensors[n["gate_weight"]]
+            pad = -(self.gate_at + self.heads) % 8
+            weights += [gate_w, gate_w.new_zeros((pad, gate_w.shape[1]))]
             if bias is not None:
-                bias = torch.cat([bias, torch.zeros(self.heads, dtype=bias.dtype, device=bias.device)])
+                bias = torch.cat([bias, torch.zeros(self.heads + pad, dtype=bias.dtype, device=bias.device)])
         self.proj = Linear(torch.cat(weights, 0).contiguous(), bias, ctx.ops)
         self.q_norm = tensors[n["q_norm"]] if params.get("head_norm") else None
         self.k_norm = tensors[n["k_norm"]] if params.get("head_norm") else None

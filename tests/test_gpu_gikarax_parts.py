@@ -153,12 +153,15 @@ def test_rotation_with_scaled_frequencies(ops, dtype, rot):
     (4, 2, 12, 20, 9, 8, 30.0), (2, 1, 16, 16, 21, 4, 200.0), (3, 3, 5, 3, 1, 4, 25.0), (2, 2, 32, 8, 64, 16, 50.0),
     (1, 1, 40, 40, None, 16, None), (6, 3, 64, 64, 36, 16, 50.0), (2, 1, 128, 128, 130, 64, 40.0),
     (6, 2, 64, 64, 40, 16, 2.0)])
+@pytest.mark.parametrize("aligned", [True, False])
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_capped_attention_with_a_sink_and_planted_keys(ops, dtype, case):
+def test_capped_attention_with_a_sink_and_planted_keys(ops, dtype, case, aligned):
     """Prompt portions and single tokens whose queries point at one scaled key each: the oldest
     key the window keeps, the one just before it (which must not be seen), the key a page border
     back, the very first key of the sequence, the token itself.  Scores are capped, the softmax
-    has one more in its denominator and every head's output is gated."""
+    has one more in its denominator and every head's output is gated.  `aligned`: rows of a
+    multiple of 16 bytes, which lets bfloat16 heads of 64 and 128 run the tensor-core kernels
+    (prompt portions fed by TMA, single tokens split over their keys); else the kernel for any size."""
     nq, nkv, hd, vd, window, ps, cap = case
     g = torch.Generator().manual_seed(window or 7)
     reach = window or 10 ** 6
@@ -169,7 +172,9 @@ def test_capped_attention_with_a_sink_and_planted_keys(ops, dtype, case):
     view = steps.mgr.view(0).paged
     for t in (view.keys, view.values):
         t.copy_(torch.randn(t.shape, generator=g).to(dtype))
-    width = (nq + nkv) * hd + nkv * vd + nq                     # the gate's logits at the end
+    gate_at = (nq + nkv) * hd + nkv * vd                          # the gate's logits behind v
+    width = gate_at + nq
+    width += (-width % 8) if aligned else (1 if width % 8 == 0 else 0)
     qkv = torch.randn((batch.num_tokens, width), generator=g).to(dtype)
     table = batch.groups[0].block_table.cpu()
     planted = 0
@@ -191,7 +196,7 @@ def test_capped_attention_with_a_sink_and_planted_keys(ops, dtype, case):
     assert planted > 10 or (cap is not None and cap < 10)
     qkv = qkv.cuda()
     sinks = torch.zeros(nq, dtype=torch.float32, device="cuda")
-    gate = qkv[:, width - nq:]
+    gate = qkv[:, gate_at:gate_at + nq]
     out = torch.empty((batch.num_tokens, nq * vd), dtype=dtype, device="cuda")
     ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd, 0.4, window, out,
                         storage=view.storage, value_dim=vd, gate=gate, gate_per_head=True, softcap=cap,
