@@ -132,7 +132,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                         long long v_row0, const int* __restrict__ block_table, int bt_stride,
                         const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                         const int* __restrict__ tiles, int nq, int nkv, int page_size,
-                        float scale_log2e, int window, __nv_bfloat16* __restrict__ out,
+                        float scale_log2e, int window, float cap_in, float cap_out,
+                        const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out,
                         int n_q_tiles) {
     constexpr int HALVES = HD / 64;
     constexpr int QTILE = HALVES * kFaHalf;              // bytes of the Q tile
@@ -346,6 +347,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
 #pragma unroll
             for (int j = 0; j < 64; ++j) {
                 float x = __uint_as_float(j < 32 ? ra[j] : rb[j - 32]);
+                // a capped score is brought to base-2 units here (the same for the whole CTA)
+                if (cap_out != 0.f) x = score_log2(x, scale_log2e, cap_in, cap_out);
                 if (!tile_inner) {
                     // key in [lo, pos] as one unsigned comparison
                     const unsigned d = static_cast<unsigned>(kb + j - lo);
@@ -355,7 +358,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 mx[j & 3] = fmaxf(mx[j & 3], x);
             }
             // the scale is positive, so the maximum is taken over the raw scores and scaled once
-            const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2e;
+            const float sc = cap_out != 0.f ? 1.0f : scale_log2e;
+            const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sc;
             // This tile's P buffer was last read by the products of tile t - 2.  They were
             // issued before the scores of tile t, and a commit covers everything issued before
             // it, so the wait for S(t) has covered them already.
@@ -395,8 +399,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 uint32_t pk[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const float p0 = fast_exp2(fmaf(sv[ch * 8 + 2 * j], scale_log2e, neg_m));
-                    const float p1 = fast_exp2(fmaf(sv[ch * 8 + 2 * j + 1], scale_log2e, neg_m));
+                    const float p0 = fast_exp2(fmaf(sv[ch * 8 + 2 * j], sc, neg_m));
+                    const float p1 = fast_exp2(fmaf(sv[ch * 8 + 2 * j + 1], sc, neg_m));
                     ps[0] += p0;
                     ps[1] += p1;
                     pk[j] = pack_bf16(p0, p1);
@@ -428,7 +432,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         const float mm = fmaxf(m, m_o);
         const float w_me = m == -INFINITY ? 0.f : fast_exp2(m - mm);
         const float w_ot = m_o == -INFINITY ? 0.f : fast_exp2(m_o - mm);
-        const float inv = 1.0f / (w_me * l + w_ot * l_o);
+        // a sink: one more score in the denominator, without a value
+        const float sink = (sinks != nullptr && mm != -INFINITY)
+                               ? fast_exp2(sinks[head] * 1.4426950408889634f - mm) : 0.f;
+        const float inv = 1.0f / (w_me * l + w_ot * l_o + sink);
         const float a_me = w_me * inv, a_ot = w_ot * inv;
         __nv_bfloat16* dst = out + static_cast<size_t>(row0 + row) * nq * HD + head * HD + half * (HD / 2);
 #pragma unroll
@@ -463,14 +470,18 @@ template <int HD>
 int launch_prefill_tc(const CUtensorMap* q_map, const CUtensorMap* kv_map, long long k_row0,
                       long long v_row0, const int* block_table, int bt_stride, const int* cu_q,
                       const int* ctx_len, const int* tiles, int n_tiles, int nq, int nkv,
-                      int page_size, float scale, int window, void* out, cudaStream_t stream) {
+                      int page_size, float scale, int window, float softcap, const float* sinks,
+                      void* out, cudaStream_t stream) {
     const size_t smem = (HD / 64) * kFaHalf + 2 * fa_stages(HD) * (HD / 64) * kFaKvHalf + 4 * kFaHalf + 1024;
     cudaFuncSetAttribute(paged_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
     dim3 grid(static_cast<unsigned>(nq) * n_tiles);
     launch_pdl(paged_prefill_tc_kernel<HD>, grid, dim3(kFaThreads), smem, stream, *q_map, *kv_map,
                k_row0, v_row0, block_table, bt_stride, cu_q, ctx_len, tiles, nq, nkv, page_size,
-               scale * 1.4426950408889634f, window, static_cast<__nv_bfloat16*>(out), n_tiles);
+               scale * 1.4426950408889634f, window,
+               softcap > 0.f ? 2.0f * 1.4426950408889634f * scale / softcap : 0.f,
+               softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, sinks,
+               static_cast<__nv_bfloat16*>(out), n_tiles);
     return launch_status();
 }
 
@@ -504,18 +515,33 @@ SOMI_API int somi_make_q_tensor_map(void* map_out, const void* qkv, long long to
 }
 
 // `tiles`: int32 [n_tiles, 3] = (request, first row, rows <= 128) over the multi-token requests.
-SOMI_API int somi_paged_attention_prefill_tc(
+// `softcap` > 0: scores pass softcap * tanh(score / softcap); `sinks`: float32 [nq] scores that
+// join every softmax's denominator, or null.
+SOMI_API int somi_paged_attention_prefill_tc_shaped(
     const void* q_map, const void* kv_map, long long k_row0, long long v_row0,
     const int* block_table, int bt_stride, const int* cu_q, const int* ctx_len, const int* tiles,
-    int n_tiles, int nq, int nkv, int hd, int page_size, float scale, int window, void* out,
-    cudaStream_t stream) {
+    int n_tiles, int nq, int nkv, int hd, int page_size, float scale, int window, float softcap,
+    const float* sinks, void* out, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!somi_prefill_tc_supported(nq, nkv, hd, page_size) ) return SOMI_ERR_UNSUPPORTED;
     const CUtensorMap* qm = static_cast<const CUtensorMap*>(q_map);
     const CUtensorMap* km = static_cast<const CUtensorMap*>(kv_map);
     if (hd == 64)
         return launch_prefill_tc<64>(qm, km, k_row0, v_row0, block_table, bt_stride, cu_q, ctx_len,
-                                     tiles, n_tiles, nq, nkv, page_size, scale, window, out, stream);
+                                     tiles, n_tiles, nq, nkv, page_size, scale, window, softcap,
+                                     sinks, out, stream);
     return launch_prefill_tc<128>(qm, km, k_row0, v_row0, block_table, bt_stride, cu_q, ctx_len, tiles,
-                                  n_tiles, nq, nkv, page_size, scale, window, out, stream);
+                                  n_tiles, nq, nkv, page_size, scale, window, softcap, sinks, out,
+                                  stream);
+}
+
+SOMI_API int somi_paged_attention_prefill_tc(
+    const void* q_map, const void* kv_map, long long k_row0, long long v_row0,
+    const int* block_table, int bt_stride, const int* cu_q, const int* ctx_len, const int* tiles,
+    int n_tiles, int nq, int nkv, int hd, int page_size, float scale, int window, void* out,
+    cudaStream_t stream) {
+    return somi_paged_attention_prefill_tc_shaped(q_map, kv_map, k_row0, v_row0, block_table,
+                                                  bt_stride, cu_q, ctx_len, tiles, n_tiles, nq, nkv,
+                                                  hd, page_size, scale, window, 0.f, nullptr, out,
+                                                  stream);
 }

@@ -531,7 +531,7 @@ __global__ void add_concat_kernel(const float* __restrict__ residual, const TD* 
     const float* r = residual + row * H;
     const float* tl = tail + row * H;
     TO* o = out + row * 2 * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x) {
         float v = r[i];
         if (delta != nullptr) {
             float sum = to_float(delta[row * H + i]);
@@ -554,7 +554,8 @@ SOMI_API int somi_add_concat(const float* residual, const void* delta, int delta
     const int threads = min(256, ((H + 31) / 32) * 32);
     if (!delta) delta_dtype = out_dtype;
 #define SOMI_LAUNCH_AC(TD, TO)                                                                   \
-    launch_pdl(add_concat_kernel<TD, TO>, dim3(T), dim3(threads), 0, stream, residual,           \
+    launch_pdl(add_concat_kernel<TD, TO>, dim3(T, T <= 256 ? (H + threads - 1) / threads : 1),   \
+               dim3(threads), 0, stream, residual,                                               \
                static_cast<const TD*>(delta), splits, split_stride, extra, tail,                 \
                static_cast<TO*>(out), H)
     if (out_dtype == SOMI_F32) {

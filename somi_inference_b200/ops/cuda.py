@@ -303,9 +303,9 @@ class CudaOps:
         with `gate_per_head` the logits are [T, nq], one per token and head.  `softcap`: scores
         pass cap * tanh(score / cap); `sinks`: float32 [nq] scores that join the softmax's
         denominator without a key.  With capped scores or sinks, bfloat16 prompt portions of head
-        sizes 64/128 run the `mma.sync` kernel that TMA feeds and single tokens the cp.async
-        split-KV kernel (the tcgen05 kernels compute neither); a per-head gate is then a kernel
-        of its own behind them.
+        sizes 64/128 run the one-tile tcgen05 kernel (or the `mma.sync` kernel that TMA feeds) and
+        single tokens the cp.async split-KV kernel; a per-head gate is then a kernel of its own
+        behind them.
         """
         _check(qkv, kcache, vcache, out, group.block_table)
         assert kcache.dtype == qkv.dtype
@@ -331,10 +331,15 @@ class CudaOps:
         split = plain and n_decode > 0 and self.decode_supported(nq, nkv, hd, qkv.dtype)
         tensor_core_prefill = (plain and batch.num_prefill_requests > 0
                                and self.prefill_supported(nq, nkv, hd, qkv.dtype))
-        if shaped and tensor_core_prefill:      # only the TMA-fed mma.sync kernel shapes scores
-            tensor_core_prefill = (self.use_tma_prefill and storage is not None and bool(
-                self.lib.somi_prefill_tma_supported(ctypes.c_int(nq), ctypes.c_int(nkv),
-                                                    ctypes.c_int(hd), ctypes.c_int(page_size))))
+        shaped_tc = False
+        if shaped and tensor_core_prefill:
+            # two kernels shape scores: the one-tile tcgen05 kernel and the TMA-fed mma.sync one
+            geometry = (ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size))
+            shaped_tc = (self.use_tc_prefill and storage is not None
+                         and bool(self.lib.somi_prefill_tc_supported(*geometry)))
+            tensor_core_prefill = shaped_tc or (
+                self.use_tma_prefill and storage is not None
+                and bool(self.lib.somi_prefill_tma_supported(*geometry)))
         # the tensor-core kernels take the mask as one number: n > 0 a window, n < 0 a chunk of -n
         if chunk:
             win = -chunk
@@ -348,7 +353,20 @@ class CudaOps:
             row_bytes = hd * 2
             # (the two-tile kernel has half as many CTAs: below one per SM the one-tile kernel,
             # with twice as many, is the faster: 0.5B shape at 2,048 tokens 123 vs 148 TFLOP/s)
-            if shaped:
+            if shaped_tc:
+                tiles = batch.tiles[self.prefill_tc_q_tile]
+                rc = self.lib.somi_paged_attention_prefill_tc_shaped(
+                    ctypes.c_void_p(self._q_tensor_map(qkv)),
+                    ctypes.c_void_p(self._kv_tensor_map(storage, hd, page_size)),
+                    ctypes.c_longlong((kcache.data_ptr() - storage.data_ptr()) // row_bytes),
+                    ctypes.c_longlong((vcache.data_ptr() - storage.data_ptr()) // row_bytes),
+                    _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
+                    _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]), *sizes,
+                    ctypes.c_float(scale), ctypes.c_int(win), ctypes.c_float(cap), _ptr(sinks),
+                    _ptr(out), self._stream())
+                self._done(rc, "paged_attention_prefill_tc")
+                kernel = "attention_prefill_tcgen05"
+            elif shaped:
                 tiles = batch.tiles[self.prefill_q_tile]
                 rc = self.lib.somi_paged_attention_prefill_tma_shaped(
                     ctypes.c_void_p(self._kv_tensor_map(storage, hd, page_size)), _ptr(qkv),

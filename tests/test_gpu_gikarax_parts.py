@@ -197,20 +197,30 @@ def test_capped_attention_with_a_sink_and_planted_keys(ops, dtype, case, aligned
     qkv = qkv.cuda()
     sinks = torch.zeros(nq, dtype=torch.float32, device="cuda")
     gate = qkv[:, gate_at:gate_at + nq]
-    out = torch.empty((batch.num_tokens, nq * vd), dtype=dtype, device="cuda")
-    ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd, 0.4, window, out,
-                        storage=view.storage, value_dim=vd, gate=gate, gate_per_head=True, softcap=cap,
-                        sinks=sinks)
-    ops.check_errors()
+    wants = {}
     for j, r in enumerate(batch.host.requests):
         first, q, c = where[r]
         keys, values = gather_cache(view, table[j], c + q, ps)
         qs = torch.zeros((c + q, nq, hd), dtype=torch.float64)
         qs[c:] = qkv[first:first + q, :nq * hd].double().cpu().reshape(q, nq, hd)
         want = plain.masked_attention(qs, keys, values, 0.4, window, cap, sink=True)[c:]
-        want = want * torch.sigmoid(gate[first:first + q].double().cpu())[:, :, None]
-        err = (out[first:first + q].double().cpu() - want.reshape(q, nq * vd)).abs().max().item()
-        assert err < tol(dtype, 4e-5, 4e-2), (r, c, q, err)
+        wants[r] = (want * torch.sigmoid(gate[first:first + q].double().cpu())[:, :, None]).reshape(q, nq * vd)
+    # the tcgen05 kernel, then the one that TMA feeds (sizes that neither takes run the kernel for
+    # any size whatever the switch says)
+    saved = ops.use_tc_prefill
+    for use_tc in ((True, False) if aligned and dtype == torch.bfloat16 and hd in (64, 128) else (True,)):
+        out = torch.empty((batch.num_tokens, nq * vd), dtype=dtype, device="cuda")
+        ops.use_tc_prefill = use_tc
+        try:
+            ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd, 0.4, window,
+                                out, storage=view.storage, value_dim=vd, gate=gate, gate_per_head=True,
+                                softcap=cap, sinks=sinks)
+        finally:
+            ops.use_tc_prefill = saved
+        ops.check_errors()
+        for r, (first, q, c) in where.items():
+            err = (out[first:first + q].double().cpu() - wants[r]).abs().max().item()
+            assert err < tol(dtype, 4e-5, 4e-2), (r, c, q, err, use_tc)
 
 
 def test_a_learned_sink_joins_the_denominator(ops):
