@@ -82,7 +82,7 @@ POSELORN = dict(window=8192, taps=4, rank=128, experts=16, identity=4, top=3, gr
 # four are a loop that runs twice, so the stream is re-mixed with the embedding twice.  The
 # latents are Digosun's; the window is longer than the timed contexts (the attention reads what
 # the Qwen2 layer reads); the linear attention has the shape's heads at the same widths.
-GIKARAX = dict(window=8192, softcap=50.0, rank=128, tau=16.0, experts=16, top=4)
+GIKARAX = dict(window=8192, softcap=30.0, rank=128, tau=8.0, experts=16, top=4)
 CONTEXT = 2048          # cached tokens per request when decode is timed
 MAX_CONTEXT = 4096      # "benchmark at context 4096": positions the model is laid out for
 LONG_CONTEXT = 40960    # ... when the points at 8 k and 32 k cached tokens are measured too
@@ -285,10 +285,10 @@ def gikarax_config(shape: str, layers: int, positions: int) -> dict:
     window = dict(heads=H, kv_heads=G, dim=hd, vdim=hd, scale=hd ** -0.5, softcap=z["softcap"],
                   mask={"size": z["window"]},
                   rot={"dims": hd // 2, "base": q["rope_theta"],
-                       "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
+                       "scaling": {"factor": 4.0, "low": 1.0, "high": 2.0, "original": 4096}})
     left = dict(heads=H, kv_heads=G, dim=hd, vdim=hd, scale=hd ** -0.5,
                 rot={"dims": hd // 2, "base": q["rope_theta"],
-                     "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}})
+                     "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}})
     right = dict(heads=H, dim=hd, vdim=hd, tau=z["tau"], decay_rank=z["rank"])
     moe = {"kind": "moe", "expert": {"ff": q["intermediate_size"] // 4},
            "router": {"experts": z["experts"], "top": z["top"]}}

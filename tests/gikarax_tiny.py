@@ -82,15 +82,15 @@ TINY_B = dict(architecture="Gikarax", vocab=67, width=45, norm={"eps": 1e-4},
 TINY_C = dict(architecture="Gikarax", vocab=257, width=96, norm={"eps": 1e-6},
               loop={"start": 0, "stop": 3, "times": 3},
               layers=[layer("latent_attention", latent(4, 24, 24, 128, 104, 0.3), moe(6, 3, 32)),
-                      layer("attention", windowed(4, 2, 32, 32, 0.5, 64, 20.0, (32, 1e6), (8.0, 1.0, 4.0, 128)),
+                      layer("attention", windowed(4, 2, 32, 32, 0.5, 64, 20.0, (32, 1e6), (6.0, 1.0, 3.0, 128)),
                             moe(4, 2, 40)),
                       layer("parallel", pair(causal(6, 6, 16, 16, 0.75, (16, 100.0)),
-                                             gated_linear(6, 8, 8, 16.0, rank=8)), moe(8, 4, 24))])
+                                             gated_linear(6, 8, 8, 12.0, rank=8)), moe(8, 5, 24))])
 TINY_D = dict(architecture="Gikarax", vocab=300, width=128, norm={"eps": 1e-6},
               loop={"start": 1, "stop": 2, "times": 2},
-              layers=[layer("attention", windowed(4, 2, 64, 64, 0.3, 48, 50.0, (32, 1e4), (8.0, 1.0, 4.0, 256)),
+              layers=[layer("attention", windowed(4, 2, 64, 64, 0.3, 48, 35.0, (48, 1e4), (4.0, 1.0, 2.0, 256)),
                             moe(4, 2, 64)),
-                      layer("parallel", pair(causal(4, 2, 128, 128, 0.2, (64, 5e4), (8.0, 256, 32.0, 1.0)),
+                      layer("parallel", pair(causal(4, 2, 128, 128, 0.2, (64, 2e4), (5.0, 256, 24.0, 2.0)),
                                              gated_linear(2, 128, 32, 8.0, rank=16)), moe(4, 2, 64)),
                       layer("latent_attention", latent(4, 32, 64, 96, 256, 0.25), None),
                       layer("attention", windowed(2, 1, 128, 128, 0.2, 200, 15.0, (128, 1e4)), moe(3, 2, 48))])
